@@ -54,7 +54,7 @@ class Session:
         for i, e in enumerate(model.plan.schedule):
             spec = model.layers[e.layer].mixer.cache_spec()
             if e.cache_of is None and spec is not None:
-                per_token += 2 * spec.num_kv_heads * spec.head_dim * (2 if model.run_dtype == torch.bfloat16 else 4)
+                per_token += spec.num_kv_heads * (spec.head_dim + spec.value_dim) * (2 if model.run_dtype == torch.bfloat16 else 4)
         want = max_seqs * ((ctx_max + block - 1) // block)
         if model.device.type == "cuda":
             free, _ = torch.cuda.mem_get_info(model.device)

@@ -81,7 +81,8 @@ class PagePool:
 
 @dataclass
 class LayerCache:
-    """One schedule entry's keys and values: ``[num_pages, block_size, kv_heads, head_dim]`` each."""
+    """One schedule entry's keys ``[num_pages, block_size, kv_heads, head_dim]`` and values (the same, or
+    ``value_dim`` wide)."""
     group: int
     k: torch.Tensor
     v: torch.Tensor
@@ -95,19 +96,26 @@ class CacheGroup:
         self.index, self.spec, self.entries = index, spec, list(entries)
         self.block_size, self.num_pages = block_size, num_pages
         self.pool = PagePool(num_pages)
-        self.storage = torch.zeros((len(self.entries), 2, num_pages, block_size, spec.num_kv_heads, spec.head_dim),
-                                   dtype=dtype, device=device)
+        shape = (len(self.entries), num_pages, block_size, spec.num_kv_heads)
+        if spec.value_dim == spec.head_dim:
+            # keys and values of an entry side by side in one array (a kernel may fetch both through one map)
+            self.storage = torch.zeros((shape[0], 2) + shape[1:] + (spec.head_dim,), dtype=dtype, device=device)
+            self.keys, self.values = self.storage[:, 0], self.storage[:, 1]
+        else:
+            self.storage = None
+            self.keys = torch.zeros(shape + (spec.head_dim,), dtype=dtype, device=device)
+            self.values = torch.zeros(shape + (spec.value_dim,), dtype=dtype, device=device)
         self.tables: Dict[object, List[int]] = {}       # request -> page id per block, -1 = not mapped
         self.np_tables: Dict[object, np.ndarray] = {}   # the same at full width as int32, ready to be copied to the device
 
     @property
     def page_bytes(self) -> int:
-        return (len(self.entries) * 2 * self.block_size * self.spec.num_kv_heads * self.spec.head_dim
-                * self.storage.element_size())
+        return (len(self.entries) * self.block_size * self.spec.num_kv_heads * (self.spec.head_dim + self.spec.value_dim)
+                * self.keys.element_size())
 
     def layer_cache(self, entry: int) -> LayerCache:
         i = self.entries.index(entry)
-        return LayerCache(self.index, self.storage[i, 0], self.storage[i, 1])
+        return LayerCache(self.index, self.keys[i], self.values[i])
 
     def first_needed_block(self, next_pos: int) -> int:
         """Blocks before this one hold no key that a query at ``next_pos`` or later can see."""

@@ -37,14 +37,17 @@ class PartSpec:
 class LayerSpec:
     """One layer with weights of its own: a block arrangement over four parts.
 
-    ``prefix`` is the checkpoint name prefix of the layer's tensors.
+    ``prefix`` is the checkpoint name prefix of the layer's tensors.  ``ffn`` may be None (a layer that is a
+    mixer only); ``post_norm1`` / ``post_norm2`` are the norms of the sublayers' outputs in arrangements that have them.
     """
     prefix: str
     block: PartSpec
     norm1: PartSpec
     mixer: PartSpec
-    norm2: PartSpec
-    ffn: PartSpec
+    norm2: Optional[PartSpec]
+    ffn: Optional[PartSpec]
+    post_norm1: Optional[PartSpec] = None
+    post_norm2: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

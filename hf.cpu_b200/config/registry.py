@@ -2,7 +2,7 @@
 
 The reference gates on ``general.architecture`` with string compares and answers
 anything else with "architecture '%s' is not supported yet" (src/model.c:107-110).
-Here the names are ``config.json``'s ``architectures[0]`` and ``model_type``.
+Here the names are ``config.json``'s ``architectures[0]``, ``architecture`` (one name) and ``model_type``.
 """
 from __future__ import annotations
 
@@ -33,10 +33,11 @@ def resolve_architecture(d: Dict[str, Any]) -> str:
     archs = d.get("architectures")
     if isinstance(archs, list):
         names += [a for a in archs if isinstance(a, str)]
-    if isinstance(d.get("model_type"), str):
-        names.append(d["model_type"])
+    for key in ("architecture", "model_type"):
+        if isinstance(d.get(key), str):
+            names.append(d[key])
     if not names:
-        raise ConfigError("config.json: neither 'architectures' nor 'model_type' names an architecture")
+        raise ConfigError("config.json: neither 'architectures', 'architecture' nor 'model_type' names an architecture")
     for n in names:
         if n in _ARCHITECTURES:
             return n

@@ -4,7 +4,8 @@
 // lo..pos; score = dot(q, k) * scale (scale after the dot), softmax in float32, out = sum p_j v_j
 // (src/model.c:499-528, src/mathx.c:77-86).  Each warp takes every fourth key with a running
 // maximum and sum; the four partial results are merged in a fixed order, so the result depends
-// only on (lo, pos) and the values, never on what else is in the batch.
+// only on (lo, pos) and the values, never on what else is in the batch.  Value heads may have another size (dv)
+// than query/key heads (d): the output row of a head has dv elements.
 #include "common.cuh"
 
 static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
@@ -19,7 +20,7 @@ template <typename T>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_plain_kernel(const T *q, const T *k_cache, const T *v_cache, const int32_t *block_table, int max_blocks,
                        const int32_t *token_seq, const int32_t *positions, int block_size, long long num_pages,
-                       int window, float scale, T *out, int H, int G, int d, int *err)
+                       int window, float scale, T *out, int H, int G, int d, int dv, int *err)
 {
     pdl_sync();
     int t = blockIdx.x, h = blockIdx.y;
@@ -44,7 +45,8 @@ attention_plain_kernel(const T *q, const T *k_cache, const T *v_cache, const int
         int blk = j / block_size;
         long long page = blk < max_blocks ? table[blk] : -1;
         if (page < 0 || page >= num_pages) { if (lane == 0) atomicOr(err, HFB_ERR_PAGE); continue; }
-        size_t base = (((size_t)page * block_size + (j % block_size)) * G + g) * d;
+        const size_t at = ((size_t)page * block_size + (j % block_size)) * G + g;
+        const size_t base = at * d, vbase = at * dv;
         float dot = 0.f;
 #pragma unroll
         for (int i = 0; i < MAX_D_PER_LANE; i++) {
@@ -59,7 +61,7 @@ attention_plain_kernel(const T *q, const T *k_cache, const T *v_cache, const int
 #pragma unroll
         for (int i = 0; i < MAX_D_PER_LANE; i++) {
             int c = lane + 32 * i;
-            if (c < d) acc[i] = acc[i] * corr + p * to_f32(v_cache[base + c]);
+            if (c < dv) acc[i] = acc[i] * corr + p * to_f32(v_cache[vbase + c]);
         }
         m = m_new;
     }
@@ -67,7 +69,7 @@ attention_plain_kernel(const T *q, const T *k_cache, const T *v_cache, const int
 #pragma unroll
     for (int i = 0; i < MAX_D_PER_LANE; i++) {
         int c = lane + 32 * i;
-        if (c < d) s_acc[warp][c] = acc[i];
+        if (c < dv) s_acc[warp][c] = acc[i];
     }
     __syncthreads();
     float mm = -INFINITY;
@@ -79,8 +81,8 @@ attention_plain_kernel(const T *q, const T *k_cache, const T *v_cache, const int
         ll += s_l[w] * f[w];
     }
     float inv = ll > 0.f ? 1.0f / ll : 0.f;
-    T *o = out + ((size_t)t * H + h) * d;
-    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    T *o = out + ((size_t)t * H + h) * dv;
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
         float v = 0.f;
         for (int w = 0; w < ATT_WARPS; w++) v += s_acc[w][c] * f[w];
         o[c] = from_f32<T>(v * inv);
@@ -94,22 +96,22 @@ using namespace hfb;
 extern "C" int hfb_attention_plain(const void *q, const void *k_cache, const void *v_cache, int dt,
                                    const int32_t *block_table, int max_blocks, const int32_t *token_seq,
                                    const int32_t *positions, int block_size, int64_t num_pages, int window,
-                                   float scale, void *out, int T, int H, int G, int d, hfb_stream s)
+                                   float scale, void *out, int T, int H, int G, int d, int dv, hfb_stream s)
 {
     if (T <= 0) return HFB_OK;
     if (!valid_dt(dt) || H <= 0 || G <= 0 || H % G || block_size <= 0 || max_blocks <= 0 || window < 0)
         return fail(HFB_EINVAL, "attention: bad arguments (H=%d G=%d block=%d)", H, G, block_size);
-    if (d <= 0 || d > 32 * MAX_D_PER_LANE)
-        return fail(HFB_ENOTSUP, "attention: head_dim %d is not supported (1..%d)", d, 32 * MAX_D_PER_LANE);
+    if (d <= 0 || d > 32 * MAX_D_PER_LANE || dv <= 0 || dv > 32 * MAX_D_PER_LANE)
+        return fail(HFB_ENOTSUP, "attention: head sizes %d / %d are not supported (1..%d)", d, dv, 32 * MAX_D_PER_LANE);
     if (H > 65535) return fail(HFB_ENOTSUP, "attention: %d heads exceed the grid limit", H);
     dim3 grid(T, H);
     if (dt == HFB_F32)
         g_launch_err = launch_pdl(attention_plain_kernel<float>, dim3(grid), dim3(ATT_WARPS * 32), 0, (cudaStream_t)s, (const float *)q, (const float *)k_cache,
             (const float *)v_cache, block_table, max_blocks, token_seq, positions, block_size, num_pages, window, scale,
-            (float *)out, H, G, d, error_word());
+            (float *)out, H, G, d, dv, error_word());
     else
         g_launch_err = launch_pdl(attention_plain_kernel<__nv_bfloat16>, dim3(grid), dim3(ATT_WARPS * 32), 0, (cudaStream_t)s, (const __nv_bfloat16 *)q,
             (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, block_table, max_blocks, token_seq, positions,
-            block_size, num_pages, window, scale, (__nv_bfloat16 *)out, H, G, d, error_word());
+            block_size, num_pages, window, scale, (__nv_bfloat16 *)out, H, G, d, dv, error_word());
     return check_pdl_launch(g_launch_err, "attention_plain");
 }

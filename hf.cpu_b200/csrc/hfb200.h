@@ -89,11 +89,12 @@ int hfb_rope_kv_write(const void *qkv, int dt, const float *cos_sin, int n_rot, 
                       int64_t cache_slots, int T, int H, int G, int d, hfb_stream s);
 
 /* Attention of every token over its request's cached keys lo..pos (lo = max(0, pos - window + 1) when
- * window > 0, else 0), plain kernel: one block per (token, head), float32 softmax. */
+ * window > 0, else 0), plain kernel: one block per (token, head), float32 softmax.  Keys [.., G, d], values
+ * [.., G, dv], out [T, H dv]. */
 int hfb_attention_plain(const void *q, const void *k_cache, const void *v_cache, int dt,
                         const int32_t *block_table, int max_blocks, const int32_t *token_seq,
                         const int32_t *positions, int block_size, int64_t num_pages, int window, float scale,
-                        void *out, int T, int H, int G, int d, hfb_stream s);
+                        void *out, int T, int H, int G, int d, int dv, hfb_stream s);
 
 /* The same for bfloat16 with head_dim 64 or 128 and a block size that divides 64, tiled, on tensor cores.
  * Tiles (tile_seq, tile_t0 = first token index, tile_nt = tokens) cover the step's tokens; a tile holds at
@@ -137,6 +138,55 @@ int hfb_attention_tc2(const void *q, const void *k_cache, const void *v_cache, c
 
 /* out[t, f] = silu(g) * u with g = gu[t, f], u = gu[t, F + f], or, interleaved, g = gu[t, 2f], u = gu[t, 2f + 1] */
 int hfb_swiglu(const void *gu, void *out, int dt, int T, int F, int interleaved, hfb_stream s);
+
+/* Activations: codes for hfb_glu / hfb_act / the expert products. */
+enum { HFB_ACT_SILU = 0, HFB_ACT_RELU = 1, HFB_ACT_GELU_TANH = 2, HFB_ACT_RELU2 = 3, HFB_ACT_NONE = 4 };
+
+/* out[t, f] = act(g) * u, gate and up laid out as for hfb_swiglu */
+int hfb_glu(const void *gu, void *out, int dt, int T, int F, int interleaved, int act, hfb_stream s);
+
+/* out[i] = act(x[i]) (in place when out == x) */
+int hfb_act(const void *x, void *out, int dt, int64_t total, int act, hfb_stream s);
+
+/* x[i] *= scale */
+int hfb_scale(float *x, int64_t total, float scale, hfb_stream s);
+
+/* Dynamic Tanh norm: out[m, :] = tanh(alpha * x[rows ? rows[m] : m, :]) * w + b (alpha a scalar on the device). */
+int hfb_dyt(const void *x, int x_dt, const int32_t *rows, const void *alpha, const void *w, const void *b,
+            int p_dt, void *out, int out_dt, int M, int E, hfb_stream s);
+
+/* residual += dyt(y); with out != NULL also out = dyt2(residual) (the next sublayer's input). */
+int hfb_dyt_residual(const void *y, int y_dt, const void *alpha, const void *w, const void *b, int p_dt,
+                     float *residual, const void *alpha2, const void *w2, const void *b2, int p2_dt,
+                     void *out, int out_dt, int M, int E, hfb_stream s);
+
+/* The tail of a q|k|v product: src [splits, T, H d + G d + G dv] float32 partial sums (+ bias) -> rotation of the first
+ * n_rot dimensions of query and key heads -> with norm != 0, x / sqrt(mean(x^2) + eps) per head -> q_out [T, H d], keys
+ * [.., G, d] and values [.., G, dv] at cache slot slots[t].  G == 0: the row holds queries only. */
+int hfb_rope_norm_kv_write(const float *src, int splits, const void *bias, int bias_dt, const float *cos_sin,
+                           int n_rot, int n_positions, const int32_t *positions, const int32_t *slots,
+                           void *q_out, void *k_cache, void *v_cache, int out_dt, int64_t cache_slots, int T,
+                           int H, int G, int d, int dv, int norm, float eps, hfb_stream s);
+
+/* Router of a mixture of experts: z = h . w^T + b in float32; the `top` largest (lowest index first among equals)
+ * go to ids [T, top], their softmax over the chosen logits only to weights [T, top]. */
+int hfb_moe_route(const void *h, int h_dt, const void *w, const void *b, int w_dt, int T, int K, int E, int top,
+                  int32_t *ids, float *weights, hfb_stream s);
+
+/* Groups the T * top (token, choice) pairs by expert: order[p] = pair at sorted place p; tiles of at most `tile`
+ * places of one expert in tile_expert / tile_p0 / tile_n (room for hfb_moe_max_tiles entries); *n_tiles on the device. */
+int hfb_moe_max_tiles(int pairs, int E, int tile);
+int hfb_moe_sort(const int32_t *ids, int pairs, int E, int tile, int32_t *order, int32_t *tile_expert, int32_t *tile_p0,
+                 int32_t *tile_n, int32_t *n_tiles, hfb_stream s);
+
+/* Grouped product over the sorted places: out[dst(p), :] = act(a[src(p), :] . w[expert(p)]^T), w [E, N, K].
+ * src(p) = order[p] / src_div when src_div > 0, else p; dst(p) = order[p] when scatter != 0, else p. */
+int hfb_moe_gemm(const void *a, int a_dt, const void *w, int w_dt, void *out, int out_dt, int act, int N, int K,
+                 const int32_t *order, int src_div, int scatter, const int32_t *tile_expert, const int32_t *tile_p0,
+                 const int32_t *tile_n, const int32_t *n_tiles, int max_tiles, int tile, hfb_stream s);
+
+/* out[t, :] = sum_j weights[t, j] * y[t * top + j, :] in float32, j in order */
+int hfb_moe_combine(const void *y, int y_dt, const float *weights, float *out, int T, int top, int N, hfb_stream s);
 
 /* out[m] = index of the first maximum of logits[m, :] */
 int hfb_argmax(const float *logits, int32_t *out, int M, int V, hfb_stream s);

@@ -1,0 +1,263 @@
+// Mixture of experts without a trip to the host: router (float32 logits, top-k, softmax over the chosen logits),
+// grouping of the (token, choice) pairs by expert, a grouped product over the groups' tiles, and the weighted sum.
+// Every size the host needs for a launch is an upper bound (tiles <= pairs / tile + experts); the device-side tile
+// count decides which blocks work, so a step of single tokens can be replayed as a graph.
+//
+// An output row is computed from its own input row and its expert's weights only, with one fixed summation order
+// over k, and a token's choices are summed in the order the router made them: what a token gets does not depend on
+// which other tokens are in the step nor on the order of the lists.
+#include "common.cuh"
+
+static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
+
+namespace hfb {
+
+constexpr int ROUTE_WARPS = 4;
+
+// One warp per token.  smem per warp: E logits, then `top` chosen logits.
+template <typename TH, typename TW>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(const TH *h, const TW *w, const TW *b, int T, int K, int E, int top, int32_t *ids, float *weights)
+{
+    pdl_entry();
+    pdl_sync_small();
+    extern __shared__ float route_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * ROUTE_WARPS + warp;
+    if (t >= T) return;
+    float *z = route_smem + (size_t)warp * (E + top), *zc = z + E;
+    const TH *x = h + (size_t)t * K;
+    for (int e = 0; e < E; e++) {
+        const TW *wr = w + (size_t)e * K;
+        float acc = 0.f;
+        for (int k = lane; k < K; k += 32) acc = fmaf(to_f32(x[k]), to_f32(wr[k]), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) z[e] = acc + (b ? to_f32(b[e]) : 0.f);
+    }
+    __syncwarp();
+    for (int j = 0; j < top; j++) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = z[e];
+            if (v > best || (v == best && e < bi)) { best = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (bi == 0x7fffffff) bi = 0;                 // (nothing comparable left: logits that are not numbers)
+        if (lane == 0) { zc[j] = best; ids[(size_t)t * top + j] = bi; z[bi] = -INFINITY; }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        const float m = zc[0];                        // the first chosen is the largest
+        float sum = 0.f;
+        for (int j = 0; j < top; j++) { zc[j] = expf(zc[j] - m); sum += zc[j]; }
+        const float inv = 1.0f / sum;
+        for (int j = 0; j < top; j++) weights[(size_t)t * top + j] = zc[j] * inv;
+    }
+}
+
+// One block.  smem: counts[E], offsets[E], cursor[E].
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int32_t *ids, int pairs, int E, int tile, int32_t *order, int32_t *tile_expert, int32_t *tile_p0,
+                int32_t *tile_n, int32_t *n_tiles)
+{
+    pdl_entry();
+    pdl_sync_small();
+    extern __shared__ int sort_smem[];
+    int *counts = sort_smem, *offsets = counts + E, *cursor = offsets + E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) { counts[e] = 0; cursor[e] = 0; }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, n = 0;
+        for (int e = 0; e < E; e++) {
+            offsets[e] = at;
+            for (int p0 = 0; p0 < counts[e]; p0 += tile) {
+                tile_expert[n] = e;
+                tile_p0[n] = at + p0;
+                tile_n[n] = min(tile, counts[e] - p0);
+                n++;
+            }
+            at += counts[e];
+        }
+        *n_tiles = n;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < E) order[offsets[e] + atomicAdd(&cursor[e], 1)] = p;
+    }
+}
+
+constexpr int GT = 64, GK = 16;       // tile of 64 places x 64 features, 16 of k at a time
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const TA *__restrict__ a, const TW *__restrict__ w, void *out, int out_dt, int act, int N, int K,
+                const int32_t *order, int src_div, int scatter, const int32_t *tile_expert, const int32_t *tile_p0,
+                const int32_t *tile_n, const int32_t *n_tiles)
+{
+    pdl_sync();
+    const int ti = blockIdx.y;
+    if (ti >= *n_tiles) return;
+    __shared__ float sa[GK][GT + 1];
+    __shared__ float sw[GK][GT + 1];
+    __shared__ int s_src[GT], s_dst[GT];
+    const int e = tile_expert[ti], p0 = tile_p0[ti], rows = tile_n[ti];
+    const int n0 = blockIdx.x * GT;
+    if (threadIdx.x < GT) {
+        const int r = threadIdx.x;
+        int src = -1, dst = -1;
+        if (r < rows) {
+            const int p = p0 + r, pair = order[p];
+            src = src_div > 0 ? pair / src_div : p;
+            dst = scatter ? pair : p;
+        }
+        s_src[r] = src;
+        s_dst[r] = dst;
+    }
+    __syncthreads();
+    const TW *we = w + (size_t)e * N * K;
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += GK) {
+        for (int x = threadIdx.x; x < GT * GK; x += 256) {
+            const int r = x / GK, c = x % GK;
+            const int gk = k0 + c, src = s_src[r];
+            sa[c][r] = (src >= 0 && gk < K) ? to_f32(a[(size_t)src * K + gk]) : 0.f;
+        }
+        for (int x = threadIdx.x; x < GT * GK; x += 256) {
+            const int r = x / GK, c = x % GK;
+            const int gn = n0 + r, gk = k0 + c;
+            sw[c][r] = (gn < N && gk < K) ? to_f32(we[(size_t)gn * K + gk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GK; kk++) {
+            float av[4], wv[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) av[i] = sa[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) wv[j] = sw[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int dst = s_dst[ty * 4 + i];
+        if (dst < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int gn = n0 + tx * 4 + j;
+            if (gn >= N) continue;
+            float v = acc[i][j];
+            if (act == HFB_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
+            else if (act == HFB_ACT_RELU) v = fmaxf(v, 0.f);
+            else if (act == HFB_ACT_SILU) v = v / (1.0f + expf(-v));
+            else if (act == HFB_ACT_GELU_TANH) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+            store_any(out, out_dt, (size_t)dst * N + gn, v);
+        }
+    }
+}
+
+template <typename TY>
+__global__ void moe_combine_kernel(const TY *y, const float *weights, float *out, int T, int top, int N)
+{
+    pdl_entry();
+    pdl_sync_small();
+    const size_t total = (size_t)T * N;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / N;
+        const int c = (int)(i % N);
+        float acc = 0.f;
+        for (int j = 0; j < top; j++) acc = fmaf(weights[t * top + j], to_f32(y[(t * top + j) * N + c]), acc);
+        out[i] = acc;
+    }
+}
+
+}  // namespace hfb
+
+using namespace hfb;
+
+extern "C" int hfb_moe_route(const void *h, int h_dt, const void *w, const void *b, int w_dt, int T, int K, int E, int top,
+                             int32_t *ids, float *weights, hfb_stream s)
+{
+    if (T <= 0) return HFB_OK;
+    if (!valid_dt(h_dt) || !valid_dt(w_dt) || K <= 0 || E <= 0 || top <= 0 || top > E)
+        return fail(HFB_EINVAL, "moe_route: bad arguments (K=%d experts=%d top=%d)", K, E, top);
+    const size_t smem = (size_t)ROUTE_WARPS * (E + top) * sizeof(float);
+    if (smem > 48 * 1024) return fail(HFB_ENOTSUP, "moe_route: %d experts are more than the router kernel takes", E);
+    const dim3 grid((T + ROUTE_WARPS - 1) / ROUTE_WARPS), block(ROUTE_WARPS * 32);
+    cudaStream_t st = (cudaStream_t)s;
+#define LAUNCH(TH, TW) g_launch_err = launch_pdl(moe_route_kernel<TH, TW>, grid, block, smem, st, (const TH *)h, (const TW *)w, (const TW *)b, T, K, E, top, ids, weights)
+    if (h_dt == HFB_F32 && w_dt == HFB_F32) LAUNCH(float, float);
+    else if (h_dt == HFB_F32) LAUNCH(float, __nv_bfloat16);
+    else if (w_dt == HFB_F32) LAUNCH(__nv_bfloat16, float);
+    else LAUNCH(__nv_bfloat16, __nv_bfloat16);
+#undef LAUNCH
+    return check_pdl_launch(g_launch_err, "moe_route");
+}
+
+extern "C" int hfb_moe_max_tiles(int pairs, int E, int tile)
+{
+    if (pairs <= 0 || E <= 0 || tile <= 0) return 0;
+    return pairs / tile + (E < pairs ? E : pairs);
+}
+
+extern "C" int hfb_moe_sort(const int32_t *ids, int pairs, int E, int tile, int32_t *order, int32_t *tile_expert,
+                            int32_t *tile_p0, int32_t *tile_n, int32_t *n_tiles, hfb_stream s)
+{
+    if (pairs <= 0) return HFB_OK;
+    if (E <= 0 || tile <= 0) return fail(HFB_EINVAL, "moe_sort: bad arguments");
+    const size_t smem = (size_t)3 * E * sizeof(int);
+    if (smem > 48 * 1024) return fail(HFB_ENOTSUP, "moe_sort: %d experts are more than the grouping kernel takes", E);
+    g_launch_err = launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), smem, (cudaStream_t)s, ids, pairs, E, tile, order, tile_expert, tile_p0, tile_n, n_tiles);
+    return check_pdl_launch(g_launch_err, "moe_sort");
+}
+
+extern "C" int hfb_moe_gemm(const void *a, int a_dt, const void *w, int w_dt, void *out, int out_dt, int act, int N, int K,
+                            const int32_t *order, int src_div, int scatter, const int32_t *tile_expert, const int32_t *tile_p0,
+                            const int32_t *tile_n, const int32_t *n_tiles, int max_tiles, int tile, hfb_stream s)
+{
+    if (max_tiles <= 0) return HFB_OK;
+    if (!valid_dt(a_dt) || !valid_dt(w_dt) || !valid_dt(out_dt) || N <= 0 || K <= 0 || tile != GT || act < 0 || act > HFB_ACT_NONE)
+        return fail(HFB_EINVAL, "moe_gemm: bad arguments (N=%d K=%d tile=%d)", N, K, tile);
+    if (max_tiles > 65535) return fail(HFB_ENOTSUP, "moe_gemm: %d tiles exceed the grid", max_tiles);
+    const dim3 grid((N + GT - 1) / GT, max_tiles);
+    cudaStream_t st = (cudaStream_t)s;
+#define LAUNCH(TA, TW) g_launch_err = launch_pdl(moe_gemm_kernel<TA, TW>, grid, dim3(256), 0, st, (const TA *)a, (const TW *)w, out, out_dt, act, N, K, order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles)
+    if (a_dt == HFB_F32 && w_dt == HFB_F32) LAUNCH(float, float);
+    else if (a_dt == HFB_F32) LAUNCH(float, __nv_bfloat16);
+    else if (w_dt == HFB_F32) LAUNCH(__nv_bfloat16, float);
+    else LAUNCH(__nv_bfloat16, __nv_bfloat16);
+#undef LAUNCH
+    return check_pdl_launch(g_launch_err, "moe_gemm");
+}
+
+extern "C" int hfb_moe_combine(const void *y, int y_dt, const float *weights, float *out, int T, int top, int N, hfb_stream s)
+{
+    if (T <= 0) return HFB_OK;
+    if (!valid_dt(y_dt) || top <= 0 || N <= 0) return fail(HFB_EINVAL, "moe_combine: bad arguments");
+    size_t b = ((size_t)T * N + 255) / 256;
+    const unsigned blocks = (unsigned)(b > 148 * 16 ? 148 * 16 : b);
+    if (y_dt == HFB_F32) g_launch_err = launch_pdl(moe_combine_kernel<float>, dim3(blocks), dim3(256), 0, (cudaStream_t)s, (const float *)y, weights, out, T, top, N);
+    else g_launch_err = launch_pdl(moe_combine_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, (cudaStream_t)s, (const __nv_bfloat16 *)y, weights, out, T, top, N);
+    return check_pdl_launch(g_launch_err, "moe_combine");
+}

@@ -1,0 +1,107 @@
+// The tail of a q|k|v product for attention whose queries and keys are brought to unit root mean square per head
+// after the rotation, whose value heads may have another size than the key heads, and whose layer may have no
+// keys and values of its own (it reads another layer's cache): sum of split-K partials + bias -> rotation of the
+// first n_rot dimensions (pairs i, i + n_rot/2) -> x / sqrt(mean(x^2) + eps) over the head -> queries to q_out,
+// keys and values to the token's cache slot.  Everything between the float32 sums and the stores is float32.
+#include "common.cuh"
+
+static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
+
+namespace hfb {
+int *error_word();
+
+constexpr int RN_WARPS = 4;
+constexpr int RN_MAX_D = 256;
+
+// One warp per (token, head) of the row [H query heads of d | G key heads of d | G value heads of dv].
+template <typename TO>
+__global__ void __launch_bounds__(RN_WARPS * 32)
+rope_norm_kv_kernel(const float *src, int splits, const void *bias, int bias_dt, const float *cos_sin, int n_rot,
+                    int n_positions, const int32_t *positions, const int32_t *slots, TO *q_out, TO *k_cache, TO *v_cache,
+                    long long cache_slots, int T, int H, int G, int d, int dv, int norm, float eps, int *err)
+{
+    pdl_entry();
+    pdl_sync_small();
+    __shared__ float buf[RN_WARPS][RN_MAX_D];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int units = H + 2 * G;
+    const long long item = (long long)blockIdx.x * RN_WARPS + warp;
+    if (item >= (long long)T * units) return;
+    const int t = (int)(item / units), u = (int)(item % units);
+    const int C = H * d + G * d + G * dv;
+    int col0, n;
+    TO *dst;
+    bool is_value = false;
+    if (u < H) { col0 = u * d; n = d; dst = q_out + ((size_t)t * H + u) * d; }
+    else {
+        if (!slots) return;
+        const long long slot = slots[t];
+        if (slot < 0) return;
+        if (slot >= cache_slots) { if (lane == 0) atomicOr(err, HFB_ERR_SLOT); return; }
+        if (u < H + G) { col0 = H * d + (u - H) * d; n = d; dst = k_cache + ((size_t)slot * G + (u - H)) * d; }
+        else { col0 = H * d + G * d + (u - H - G) * dv; n = dv; dst = v_cache + ((size_t)slot * G + (u - H - G)) * dv; is_value = true; }
+    }
+    float *x = buf[warp];
+    const size_t plane = (size_t)T * C;
+    for (int c = lane; c < n; c += 32) {
+        float v = bias ? load_any(bias, bias_dt, col0 + c) : 0.f;
+        const float *p = src + (size_t)t * C + col0 + c;
+        float acc = 0.f;
+        for (int s = 0; s < splits; s++) acc += p[(size_t)s * plane];
+        x[c] = acc + v;
+    }
+    __syncwarp();
+    if (is_value) {
+        for (int c = lane; c < n; c += 32) dst[c] = from_f32<TO>(x[c]);
+        return;
+    }
+    const int half = n_rot / 2;
+    if (half > 0) {
+        int pos = positions[t];
+        if (pos < 0 || pos >= n_positions) { if (lane == 0) atomicOr(err, HFB_ERR_POSITION); pos = 0; }
+        const float *cs = cos_sin + (size_t)pos * half * 2;
+        for (int i = lane; i < half; i += 32) {
+            float lo, hi;
+            rope_pair(x[i], x[i + half], cs[2 * i], cs[2 * i + 1], lo, hi);
+            x[i] = lo;
+            x[i + half] = hi;
+        }
+        __syncwarp();
+    }
+    float r = 1.0f;
+    if (norm) {
+        float ss = 0.f;
+        for (int c = lane; c < n; c += 32) ss = fmaf(x[c], x[c], ss);
+        ss = warp_sum(ss);
+        r = 1.0f / sqrtf(ss / (float)n + eps);
+    }
+    for (int c = lane; c < n; c += 32) dst[c] = from_f32<TO>(x[c] * r);
+}
+
+}  // namespace hfb
+
+using namespace hfb;
+
+extern "C" int hfb_rope_norm_kv_write(const float *src, int splits, const void *bias, int bias_dt, const float *cos_sin,
+                                      int n_rot, int n_positions, const int32_t *positions, const int32_t *slots,
+                                      void *q_out, void *k_cache, void *v_cache, int out_dt, int64_t cache_slots, int T,
+                                      int H, int G, int d, int dv, int norm, float eps, hfb_stream s)
+{
+    if (T <= 0) return HFB_OK;
+    if (!valid_dt(out_dt) || (bias && !valid_dt(bias_dt)) || splits < 1 || H <= 0 || G < 0 || d <= 0 || dv <= 0 ||
+        n_rot < 0 || n_rot > d || (n_rot & 1))
+        return fail(HFB_EINVAL, "rope_norm_kv_write: bad arguments (H=%d G=%d d=%d dv=%d n_rot=%d)", H, G, d, dv, n_rot);
+    if (d > RN_MAX_D || dv > RN_MAX_D) return fail(HFB_ENOTSUP, "rope_norm_kv_write: head sizes above %d are not supported", RN_MAX_D);
+    if (n_rot > 0 && (!cos_sin || !positions)) return fail(HFB_EINVAL, "rope_norm_kv_write: rotation needs a table and positions");
+    if (G > 0 && slots && (!k_cache || !v_cache)) return fail(HFB_EINVAL, "rope_norm_kv_write: keys and values need a cache");
+    const long long items = (long long)T * (H + 2 * G);
+    const unsigned blocks = (unsigned)((items + RN_WARPS - 1) / RN_WARPS);
+    if (out_dt == HFB_F32)
+        g_launch_err = launch_pdl(rope_norm_kv_kernel<float>, dim3(blocks), dim3(RN_WARPS * 32), 0, (cudaStream_t)s, src, splits, bias, bias_dt, cos_sin, n_rot,
+            n_positions, positions, slots, (float *)q_out, (float *)k_cache, (float *)v_cache, (long long)cache_slots, T, H, G, d, dv, norm, eps, error_word());
+    else
+        g_launch_err = launch_pdl(rope_norm_kv_kernel<__nv_bfloat16>, dim3(blocks), dim3(RN_WARPS * 32), 0, (cudaStream_t)s, src, splits, bias, bias_dt, cos_sin, n_rot,
+            n_positions, positions, slots, (__nv_bfloat16 *)q_out, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, (long long)cache_slots, T, H, G, d, dv, norm, eps,
+            error_word());
+    return check_pdl_launch(g_launch_err, "rope_norm_kv_write");
+}

@@ -51,7 +51,7 @@ def step_flops(model, q_lens: Sequence[int], kv_lens: Sequence[int], logit_rows:
     total = 0.0
     for e in model.plan.schedule:
         layer = model.layers[e.layer]
-        total += layer.mixer.flops(q_lens, kv_lens) + layer.ffn.flops(sum(q_lens))
+        total += layer.mixer.flops(q_lens, kv_lens) + (layer.ffn.flops(sum(q_lens)) if layer.ffn is not None else 0.0)
     return total + model.head.flops(logit_rows)
 
 

@@ -161,13 +161,18 @@ def attention_step_arrays(q_lens, heads_per_group: int):
     return out
 
 
-def paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tiles=None) -> None:
+def paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tiles=None, dv=None) -> None:
     """``tiles``: the device arrays of :func:`attention_step_arrays` for this step (without them only the plain
-    kernel runs)."""
-    check_head_dim(d)
-    _need(q.shape[1] == H * d and out.shape == q.shape, "attention: shape mismatch")
+    kernel runs).  ``dv``: the size of a value head where it is not ``d``; ``out`` is then [T, H * dv]."""
+    dv = d if dv is None else int(dv)
+    _need(0 < d <= MAX_HEAD_DIM and 0 < dv <= MAX_HEAD_DIM, "attention: head sizes must be 1..%d" % MAX_HEAD_DIM)
+    _need(q.shape[1] == H * d and out.shape == (q.shape[0], H * dv), "attention: shape mismatch")
+    _need(k_cache.shape[2:] == (G, d) and v_cache.shape[2:] == (G, dv), "attention: cache geometry mismatch")
     _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype, "attention: element types differ")
-    backend().paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, int(window), float(scale), out, tiles or {})
+    if dv == d:
+        backend().paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, int(window), float(scale), out, tiles or {})
+    else:
+        backend().paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, int(window), float(scale), out, tiles or {}, dv=dv)
 
 
 def swiglu(gu: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
@@ -200,6 +205,122 @@ def linear_rope_kv(a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out,
     _need(k_cache.shape[2:] == (G, d) and v_cache.shape == k_cache.shape and k_cache.dtype == q_out.dtype,
           "linear_rope_kv: cache geometry mismatch")
     backend().linear_rope_kv(a, w, bias, qkv_buf, cos_sin, int(n_rot), positions, slots, q_out, k_cache, v_cache, H, G, d)
+
+
+ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "relu2": 3, "none": 4}       # relu2: the square of relu
+MOE_TILE = 64               # places of one expert per tile of the grouped product
+
+
+def _act(name: str) -> int:
+    if name not in ACTIVATIONS:
+        raise UnsupportedError(f"activation '{name}' is not supported (known: {', '.join(ACTIVATIONS)})")
+    return ACTIVATIONS[name]
+
+
+def _dyt_ok(p, E, what):
+    alpha, w, b = p
+    _need(alpha.numel() == 1 and w.shape == (E,) and b.shape == (E,) and alpha.dtype == w.dtype == b.dtype,
+          f"{what}: norm parameters must be a scalar and two vectors [E] of one type")
+
+
+def dyt(x: torch.Tensor, params, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """Dynamic Tanh norm: out = tanh(alpha * x) * w + b, ``params`` = (alpha, w, b); with ``rows`` (int32) only
+    those rows of ``x``, in that order."""
+    _need(x.dim() == 2 and out.shape[1] == x.shape[1], "dyt: width mismatch")
+    _dyt_ok(params, x.shape[1], "dyt")
+    _need(rows is None or (rows.dtype == torch.int32 and rows.shape[0] == out.shape[0]), "dyt: rows must be int32 [M]")
+    _need(rows is not None or out.shape[0] == x.shape[0], "dyt: row count mismatch")
+    backend().dyt(x, params, out, rows)
+
+
+def dyt_residual(y: torch.Tensor, post, residual: torch.Tensor, nxt=None, out: Optional[torch.Tensor] = None) -> None:
+    """residual += dyt_post(y); with ``nxt`` and ``out`` also out = dyt_nxt(residual)."""
+    _need(residual.dtype == torch.float32 and y.shape == residual.shape, "dyt_residual: shape mismatch")
+    _dyt_ok(post, y.shape[1], "dyt_residual")
+    _need((nxt is None) == (out is None), "dyt_residual: the next norm and its output come together")
+    if nxt is not None:
+        _dyt_ok(nxt, y.shape[1], "dyt_residual")
+        _need(out.shape == residual.shape, "dyt_residual: output shape mismatch")
+    backend().dyt_residual(y, post, residual, nxt, out)
+
+
+def linear_rope_norm_kv(a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d, dv,
+                        norm_eps) -> None:
+    """The q|k|v product and its tail for attention with unit-rms queries and keys: row = [H heads of d | G key heads
+    of d | G value heads of dv] (G = 0: the layer has no keys and values of its own); rotation of the first ``n_rot``
+    dimensions of query and key heads, then, unless ``norm_eps`` is None, x / sqrt(mean(x^2) + eps) per head; queries
+    to ``q_out``, keys and values to the cache at ``slots``.  ``qkv_buf`` [T, row] float32 is scratch."""
+    C = H * d + G * (d + dv)
+    _need(w.shape[0] == C and q_out.shape == (a.shape[0], H * d) and a.shape[1] == w.shape[1], "linear_rope_norm_kv: shape mismatch")
+    _need(qkv_buf.shape == (a.shape[0], C) and qkv_buf.dtype == torch.float32, "linear_rope_norm_kv: scratch must be float32 [T, row]")
+    _need(0 < d <= MAX_HEAD_DIM and 0 < dv <= MAX_HEAD_DIM and n_rot % 2 == 0 and 0 <= n_rot <= d, "linear_rope_norm_kv: bad head sizes")
+    if G:
+        _need(k_cache.shape[2:] == (G, d) and v_cache.shape[2:] == (G, dv) and k_cache.dtype == q_out.dtype == v_cache.dtype,
+              "linear_rope_norm_kv: cache geometry mismatch")
+    _need(n_rot == 0 or (cos_sin is not None and cos_sin.shape[1:] == (n_rot // 2, 2) and cos_sin.dtype == torch.float32),
+          "linear_rope_norm_kv: cos/sin table must be float32 [positions, n_rot/2, 2]")
+    backend().linear_rope_norm_kv(a, w, bias, qkv_buf, cos_sin, int(n_rot), positions, slots, q_out, k_cache, v_cache,
+                                  H, G, d, dv, None if norm_eps is None else float(norm_eps))
+
+
+def linear_glu(a: torch.Tensor, w: torch.Tensor, gu_buf: torch.Tensor, out: torch.Tensor, act: str) -> None:
+    """out = act(g) * u where [g0, u0, g1, u1, ...] = a @ w.T (rows of ``w`` alternate gate, up)."""
+    _need(a.shape[1] == w.shape[1] and w.shape[0] == 2 * out.shape[1] and out.shape[0] == a.shape[0], "linear_glu: shape mismatch")
+    _need(gu_buf.shape == (a.shape[0], w.shape[0]), "linear_glu: scratch must be [M, 2F]")
+    if act == "silu":
+        backend().linear_swiglu(a, w, gu_buf, out)
+    else:
+        backend().linear_glu(a, w, gu_buf, out, _act(act))
+
+
+def linear_act(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: str) -> None:
+    """out = act(a @ w.T)."""
+    _need(a.shape[1] == w.shape[1] and out.shape == (a.shape[0], w.shape[0]), "linear_act: shape mismatch")
+    backend().linear_act(a, w, out, _act(act))
+
+
+def scale_(x: torch.Tensor, s: float) -> None:
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "scale_: float32, contiguous")
+    backend().scale_(x, float(s))
+
+
+def moe_route(h, w, b, top: int, ids, weights) -> None:
+    """Router: z = h @ w.T + b in float32; the ``top`` largest logits of a token choose its experts (``ids`` int32
+    [T, top], largest first, the lower index among equals), ``weights`` = softmax over the chosen logits only."""
+    T, E = h.shape[0], w.shape[0]
+    _need(h.shape[1] == w.shape[1] and (b is None or b.shape == (E,)) and 1 <= top <= E, "moe_route: shape mismatch")
+    _need(ids.shape == (T, top) and ids.dtype == torch.int32 and weights.shape == (T, top) and weights.dtype == torch.float32,
+          "moe_route: ids int32 [T, top], weights float32 [T, top]")
+    backend().moe_route(h, w, b, int(top), ids, weights)
+
+
+def moe_max_tiles(pairs: int, experts: int) -> int:
+    """Room for the tile lists of :func:`moe_group`: no grouping of ``pairs`` places over ``experts`` has more tiles."""
+    return pairs // MOE_TILE + min(experts, pairs)
+
+
+def moe_group(ids, experts: int, order, tile_expert, tile_p0, tile_n, n_tiles) -> None:
+    """Groups the (token, choice) pairs of ``ids`` [T, top] by expert, on the device: ``order[p]`` = the pair at
+    place p; tiles of at most MOE_TILE places of one expert; their number in ``n_tiles`` [1]."""
+    pairs = ids.numel()
+    _need(order.numel() >= pairs and min(tile_expert.numel(), tile_p0.numel(), tile_n.numel()) >= moe_max_tiles(pairs, experts)
+          and n_tiles.numel() >= 1, "moe_group: lists too short")
+    backend().moe_group(ids, int(experts), order, tile_expert, tile_p0, tile_n, n_tiles)
+
+
+def moe_gemm(a, w, out, act: str, order, src_div: int, scatter: bool, tile_expert, tile_p0, tile_n, n_tiles, pairs: int) -> None:
+    """Grouped product over the places of :func:`moe_group`: out[dst(p)] = act(a[src(p)] @ w[expert(p)].T) with
+    w [E, N, K]; src(p) = order[p] // src_div if src_div else p; dst(p) = order[p] if scatter else p."""
+    _need(w.dim() == 3 and a.shape[1] == w.shape[2] and out.shape[1] == w.shape[1], "moe_gemm: shape mismatch")
+    backend().moe_gemm(a, w, out, _act(act), order, int(src_div), bool(scatter), tile_expert, tile_p0, tile_n, n_tiles,
+                       moe_max_tiles(int(pairs), w.shape[0]))
+
+
+def moe_combine(y, weights, out) -> None:
+    """out[t] = sum_j weights[t, j] * y[t * top + j] in float32, j in order."""
+    T, top = weights.shape
+    _need(y.shape == (T * top, out.shape[1]) and out.shape[0] == T and out.dtype == torch.float32, "moe_combine: shape mismatch")
+    backend().moe_combine(y, weights, out)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -140,10 +140,11 @@ class NativeBackend:
                                                c_int64(cache_slots), c_int(T), c_int(H), c_int(G), c_int(d),
                                                self._stream()), "rope_kv_write")
 
-    def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tile_arrays):
+    def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tile_arrays, dv=None):
         self._on_gpu(q, k_cache, v_cache, meta.block_table, ctx.token_seq, ctx.positions, out)
         T = q.shape[0]
-        if (self.attention == "fast" and tile_arrays and q.dtype == torch.bfloat16 and d in (64, 128)
+        dv = d if dv is None else dv
+        if (self.attention == "fast" and tile_arrays and q.dtype == torch.bfloat16 and d in (64, 128) and dv == d
                 and 64 % meta.block_size == 0):
             decode = ctx.max_q_len == 1
 
@@ -232,7 +233,7 @@ class NativeBackend:
         self._check(self.lib.hfb_attention_plain(_p(q), _p(k_cache), _p(v_cache), c_int(_dt(q)), _p(meta.block_table),
                                                  c_int(meta.max_blocks), _p(ctx.token_seq), _p(ctx.positions),
                                                  c_int(meta.block_size), c_int64(k_cache.shape[0]), c_int(window),
-                                                 c_float(scale), _p(out), c_int(T), c_int(H), c_int(G), c_int(d),
+                                                 c_float(scale), _p(out), c_int(T), c_int(H), c_int(G), c_int(d), c_int(dv),
                                                  self._stream()), "attention")
 
     def swiglu(self, gu, out, interleaved):
@@ -328,6 +329,83 @@ class NativeBackend:
             _p(ws), c_int(splits), c_int(_dt(q_out)), _p(bias), c_int(_dt(bias) if bias is not None else 0), _p(cos_sin),
             c_int(n_rot), c_int(npos), _p(positions), _p(slots), _p(q_out), _p(k_cache), _p(v_cache), c_int64(cache_slots),
             c_int(M), c_int(H), c_int(G), c_int(d), self._stream()), "reduce_rope_kv")
+
+    # ---- Dynamic Tanh norms, unit-rms heads, gated and routed feed-forwards --------------------------------
+    def dyt(self, x, params, out, rows):
+        alpha, w, b = params
+        self._on_gpu(x, alpha, w, b, out, rows)
+        M, E = out.shape
+        self._check(self.lib.hfb_dyt(_p(x), c_int(_dt(x)), _p(rows), _p(alpha), _p(w), _p(b), c_int(_dt(w)), _p(out),
+                                     c_int(_dt(out)), c_int(M), c_int(E), self._stream()), "dyt")
+
+    def dyt_residual(self, y, post, residual, nxt, out):
+        self._on_gpu(y, *post, residual, out, *(nxt or ()))
+        M, E = residual.shape
+        n = nxt or (None, None, None)
+        self._check(self.lib.hfb_dyt_residual(
+            _p(y), c_int(_dt(y)), _p(post[0]), _p(post[1]), _p(post[2]), c_int(_dt(post[1])), _p(residual), _p(n[0]), _p(n[1]),
+            _p(n[2]), c_int(_dt(n[1]) if nxt else 0), _p(out), c_int(_dt(out) if out is not None else 0), c_int(M), c_int(E),
+            self._stream()), "dyt_residual")
+
+    def linear_rope_norm_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d, dv,
+                            norm_eps):
+        self._on_gpu(a, w, bias, cos_sin, positions, slots, q_out, k_cache, v_cache)
+        T = a.shape[0]
+        part = self._partials(a, w) if self._tc_ok(a, w) else None
+        if part is None:
+            self.linear(a, w, bias, qkv_buf, False)
+            src, splits, bias = qkv_buf, 1, None
+        else:
+            src, splits = part
+        cache_slots = k_cache.shape[0] * k_cache.shape[1] if G else 0
+        self._check(self.lib.hfb_rope_norm_kv_write(
+            _p(src), c_int(splits), _p(bias), c_int(_dt(bias) if bias is not None else 0), _p(cos_sin), c_int(n_rot),
+            c_int(cos_sin.shape[0] if cos_sin is not None else 0), _p(positions), _p(slots if G else None), _p(q_out),
+            _p(k_cache if G else None), _p(v_cache if G else None), c_int(_dt(q_out)), c_int64(cache_slots), c_int(T), c_int(H),
+            c_int(G), c_int(d), c_int(dv), c_int(0 if norm_eps is None else 1), c_float(norm_eps or 0.0), self._stream()),
+            "rope_norm_kv_write")
+
+    def linear_glu(self, a, w, gu_buf, out, act):
+        self._on_gpu(a, w, gu_buf, out)
+        self.linear(a, w, None, gu_buf, False)
+        T, F = out.shape
+        self._check(self.lib.hfb_glu(_p(gu_buf), _p(out), c_int(_dt(out)), c_int(T), c_int(F), c_int(1), c_int(act),
+                                     self._stream()), "glu")
+
+    def linear_act(self, a, w, out, act):
+        self._on_gpu(a, w, out)
+        self.linear(a, w, None, out, False)
+        self._check(self.lib.hfb_act(_p(out), _p(out), c_int(_dt(out)), c_int64(out.numel()), c_int(act), self._stream()), "act")
+
+    def scale_(self, x, s):
+        self._on_gpu(x)
+        self._check(self.lib.hfb_scale(_p(x), c_int64(x.numel()), c_float(s), self._stream()), "scale")
+
+    def moe_route(self, h, w, b, top, ids, weights):
+        self._on_gpu(h, w, b, ids, weights)
+        T, K = h.shape
+        self._check(self.lib.hfb_moe_route(_p(h), c_int(_dt(h)), _p(w), _p(b), c_int(_dt(w)), c_int(T), c_int(K),
+                                           c_int(w.shape[0]), c_int(top), _p(ids), _p(weights), self._stream()), "moe_route")
+
+    def moe_group(self, ids, experts, order, tile_expert, tile_p0, tile_n, n_tiles):
+        self._on_gpu(ids, order, tile_expert, tile_p0, tile_n, n_tiles)
+        from . import MOE_TILE
+        self._check(self.lib.hfb_moe_sort(_p(ids), c_int(ids.numel()), c_int(experts), c_int(MOE_TILE), _p(order), _p(tile_expert),
+                                          _p(tile_p0), _p(tile_n), _p(n_tiles), self._stream()), "moe_sort")
+
+    def moe_gemm(self, a, w, out, act, order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles, max_tiles):
+        self._on_gpu(a, w, out, order, tile_expert, tile_p0, tile_n, n_tiles)
+        from . import MOE_TILE
+        self._check(self.lib.hfb_moe_gemm(_p(a), c_int(_dt(a)), _p(w), c_int(_dt(w)), _p(out), c_int(_dt(out)), c_int(act),
+                                          c_int(w.shape[1]), c_int(w.shape[2]), _p(order), c_int(src_div), c_int(1 if scatter else 0),
+                                          _p(tile_expert), _p(tile_p0), _p(tile_n), _p(n_tiles), c_int(max_tiles), c_int(MOE_TILE),
+                                          self._stream()), "moe_gemm")
+
+    def moe_combine(self, y, weights, out):
+        self._on_gpu(y, weights, out)
+        T, top = weights.shape
+        self._check(self.lib.hfb_moe_combine(_p(y), c_int(_dt(y)), _p(weights), _p(out), c_int(T), c_int(top),
+                                             c_int(out.shape[1]), self._stream()), "moe_combine")
 
     def sample(self, logits, temps, top_ks, top_ps, min_ps, uniforms, out):
         self._on_gpu(logits, temps, top_ks, top_ps, min_ps, uniforms, out)

@@ -25,9 +25,16 @@ class Layer:
     mixer: object
     norm2: object
     ffn: object
+    post1: object = None
+    post2: object = None
 
     def parts(self):
-        return (self.block, self.norm1, self.mixer, self.norm2, self.ffn)
+        return tuple(p for p in (self.block, self.norm1, self.mixer, self.post1, self.norm2, self.ffn, self.post2)
+                     if p is not None)
+
+    def post_norms(self):
+        """Keyword arguments for the block, for arrangements with norms behind the sublayers."""
+        return {"post1": self.post1, "post2": self.post2} if self.post1 is not None else {}
 
 
 class Model:
@@ -47,8 +54,10 @@ class Model:
                 block=make_part("block", ls.block),
                 norm1=make_part("norm", ls.norm1),
                 mixer=make_part("mixer", ls.mixer, positions=self.positions),
-                norm2=make_part("norm", ls.norm2),
-                ffn=make_part("ffn", ls.ffn)))
+                norm2=make_part("norm", ls.norm2) if ls.norm2 is not None else None,
+                ffn=make_part("ffn", ls.ffn) if ls.ffn is not None else None,
+                post1=make_part("norm", ls.post_norm1) if ls.post_norm1 is not None else None,
+                post2=make_part("norm", ls.post_norm2) if ls.post_norm2 is not None else None))
         self.final_norm = make_part("norm", p.final_norm)
         self.head = make_part("head", p.head)
         self.bound = False
@@ -114,7 +123,7 @@ class Model:
                 next_norm = self.final_norm if getattr(ctx, "logits_for_all", False) else None
             xn = layer.block.forward(ctx, x, layer.norm1, layer.mixer, layer.norm2, layer.ffn,
                                      ctx.entry_cache(owner), ctx.entry_state(i), e.cache_of is None,
-                                     xn_ready=xn, next_norm=next_norm)
+                                     xn_ready=xn, next_norm=next_norm, **layer.post_norms())
         M = ctx.num_logit_rows
         if M == 0:
             return None

@@ -6,6 +6,13 @@ the cache at the token's slot; head h attends with the key/value head ``h // (H/
 dot, softmax, weighted values; ``out = att Wo^T`` is added to the residual
 (src/model.c:581-609, :499-528).  q, k and v are one matrix product over concatenated rows
 (src/model.c:581-585 runs the three jobs in one pass).
+
+Options beyond the reference's layer, each a constructor argument: ``scale`` (the factor on the scores, where it is
+not ``1/sqrt(head_dim)``), ``v_head_dim`` (value heads of another size than query/key heads), ``qk_norm_eps`` (after
+the rotation every query and key head is divided by its root mean square, ``x / sqrt(mean(x^2) + eps)``, no weight;
+the cache holds the keys in that form), and ``own_kv=False`` (the layer has no key and value projections: its queries
+attend over the cache of the schedule entry it is pointed at, which a layer with the same head counts and rotation
+has filled).
 """
 from __future__ import annotations
 
@@ -24,11 +31,22 @@ class PagedAttention(Mixer):
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qkv_bias: bool, out_bias: bool, window: int, position, prefix: str,
-                 positions=None, names=None, **_):
+                 positions=None, names=None, scale=None, v_head_dim=None, qk_norm_eps=None, own_kv: bool = True,
+                 bias_suffix: str = ".bias", weight_suffix: str = ".weight", **_):
         self.E, self.H, self.G, self.d = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
         if self.H % self.G:
             raise UnsupportedError(f"unsupported attention geometry: {self.H} heads over {self.G} key/value heads")
-        kernels.check_head_dim(self.d)
+        self.dv = int(v_head_dim) if v_head_dim else self.d
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        self.own_kv = bool(own_kv)
+        # the q|k|v tail that normalises heads also takes the other two options; the reference's layer keeps its own
+        self.general = self.qk_norm_eps is not None or self.dv != self.d or not self.own_kv
+        if self.general:
+            if not (0 < self.d <= kernels.MAX_HEAD_DIM and 0 < self.dv <= kernels.MAX_HEAD_DIM):
+                raise UnsupportedError(f"head sizes {self.d} / {self.dv} are not supported (1 to {kernels.MAX_HEAD_DIM})")
+        else:
+            kernels.check_head_dim(self.d)
+        self.wsuf, self.bsuf = weight_suffix, bias_suffix
         self.qkv_bias, self.out_bias, self.window = bool(qkv_bias), bool(out_bias), int(window)
         self.rotary = (positions or {}).get(position) if position else None
         if position and self.rotary is None:
@@ -36,7 +54,7 @@ class PagedAttention(Mixer):
         n = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj"}
         n.update(names or {})
         self.names = {k: f"{prefix}.{v}" for k, v in n.items()}
-        self.scale = 1.0 / math.sqrt(self.d)
+        self.scale = 1.0 / math.sqrt(self.d) if scale is None else float(scale)
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
 
     @property
@@ -47,8 +65,16 @@ class PagedAttention(Mixer):
     def KD(self):
         return self.G * self.d
 
+    @property
+    def VD(self):
+        return self.G * self.dv
+
+    @property
+    def OD(self):
+        return self.H * self.dv
+
     def cache_spec(self):
-        return CacheSpec(self.G, self.d, self.window)
+        return CacheSpec(self.G, self.d, self.window, 0 if self.dv == self.d else self.dv)
 
     def step_arrays_key(self):
         return ("paged_attention_tiles", self.H // self.G)
@@ -57,26 +83,27 @@ class PagedAttention(Mixer):
         # the tile lists of the attention kernels: how they cut the step's tokens is the kernels' business
         return kernels.attention_step_arrays(batch.q_lens, self.H // self.G)
 
+    def _projections(self):
+        """(key of ``names``, output features) of the projections in the fused product's row order."""
+        return [("q", self.QD)] + ([("k", self.KD), ("v", self.VD)] if self.own_kv else [])
+
     def tensor_specs(self):
-        s = [TensorSpec(self.names["q"] + ".weight", (self.QD, self.E)),
-             TensorSpec(self.names["k"] + ".weight", (self.KD, self.E)),
-             TensorSpec(self.names["v"] + ".weight", (self.KD, self.E)),
-             TensorSpec(self.names["o"] + ".weight", (self.E, self.QD))]
+        s = [TensorSpec(self.names[x] + self.wsuf, (n, self.E)) for x, n in self._projections()]
+        s.append(TensorSpec(self.names["o"] + self.wsuf, (self.E, self.OD)))
         if self.qkv_bias:
-            s += [TensorSpec(self.names[x] + ".bias", (n,)) for x, n in
-                  (("q", self.QD), ("k", self.KD), ("v", self.KD))]
+            s += [TensorSpec(self.names[x] + self.bsuf, (n,)) for x, n in self._projections()]
         if self.out_bias:
-            s.append(TensorSpec(self.names["o"] + ".bias", (self.E,)))
+            s.append(TensorSpec(self.names["o"] + self.bsuf, (self.E,)))
         return s
 
     def bind(self, tensors, run_dtype, device):
         # q, k and v rows go straight into the one matrix the product reads, a tensor at a time
-        self.w_qkv = fused_rows(tensors, [self.names[x] + ".weight" for x in "qkv"], device)
+        self.w_qkv = fused_rows(tensors, [self.names[x] + self.wsuf for x, _ in self._projections()], device)
         if self.qkv_bias:
-            self.b_qkv = fused_rows(tensors, [self.names[x] + ".bias" for x in "qkv"], device)
-        self.w_o = tensors[self.names["o"] + ".weight"].contiguous()
+            self.b_qkv = fused_rows(tensors, [self.names[x] + self.bsuf for x, _ in self._projections()], device)
+        self.w_o = tensors[self.names["o"] + self.wsuf].contiguous()
         if self.out_bias:
-            self.b_o = tensors[self.names["o"] + ".bias"].contiguous()
+            self.b_o = tensors[self.names["o"] + self.bsuf].contiguous()
 
     def weight_bytes(self):
         return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.b_qkv, self.w_o, self.b_o)
@@ -90,28 +117,40 @@ class PagedAttention(Mixer):
             if self.window > 0:
                 for_all = sum(min(self.window, m - n + i + 1) for i in range(n)) if m > self.window else for_all
             seen += for_all
-        return 2.0 * T * (self.w_qkv.numel() + self.w_o.numel()) + 4.0 * self.QD * seen
+        return 2.0 * T * (self.w_qkv.numel() + self.w_o.numel()) + 2.0 * (self.QD + self.OD) * seen
 
     def _attend(self, ctx, xn, cache, write_cache):
         T = xn.shape[0]
-        qkv = ctx.buf("attn_qkv", (T, self.QD + 2 * self.KD), xn.dtype)
         q = ctx.buf("attn_q", (T, self.QD), xn.dtype)
         meta = ctx.group_meta(cache.group)
         cos_sin = self.rotary.cos_sin if self.rotary is not None else None
         n_rot = self.rotary.n_rot if self.rotary is not None else 0
-        with kernels.phase("qkv"):
-            kernels.linear_rope_kv(xn, self.w_qkv, self.b_qkv, qkv, cos_sin, n_rot, ctx.positions,
-                                   meta.slots if write_cache else None, q, cache.k, cache.v, self.H, self.G, self.d)
-        att = ctx.buf("attn_out", (T, self.QD), xn.dtype)
+        if write_cache and not self.own_kv:
+            raise ValueError("a layer without key and value projections must read another schedule entry's cache")
+        if self.general:
+            # the product's sums stay float32 until rotation and the heads' normalisation are done
+            G = self.G if self.own_kv else 0
+            qkv = ctx.buf("attn_qkv32", (T, self.QD + G * (self.d + self.dv)), torch.float32)
+            with kernels.phase("qkv"):
+                kernels.linear_rope_norm_kv(xn, self.w_qkv, self.b_qkv, qkv, cos_sin, n_rot, ctx.positions,
+                                            meta.slots if write_cache else None, q, cache.k, cache.v, self.H, G, self.d,
+                                            self.dv, self.qk_norm_eps)
+        else:
+            qkv = ctx.buf("attn_qkv", (T, self.QD + 2 * self.KD), xn.dtype)
+            with kernels.phase("qkv"):
+                kernels.linear_rope_kv(xn, self.w_qkv, self.b_qkv, qkv, cos_sin, n_rot, ctx.positions,
+                                       meta.slots if write_cache else None, q, cache.k, cache.v, self.H, self.G, self.d)
+        att = ctx.buf("attn_out", (T, self.OD), xn.dtype)
         with kernels.phase("attn"):
             kernels.paged_attention(q, cache.k, cache.v, meta, ctx, self.H, self.G, self.d,
-                                    self.window, self.scale, att, tiles=ctx.arrays(self.step_arrays_key()))
+                                    self.window, self.scale, att, tiles=ctx.arrays(self.step_arrays_key()), dv=self.dv)
         return att
 
-    def forward(self, ctx, xn, residual, cache, state, write_cache):
+    def forward(self, ctx, xn, residual, cache, state, write_cache, accumulate=True):
+        """``accumulate=False`` stores the sublayer's output in ``residual`` (float32) instead of adding it."""
         att = self._attend(ctx, xn, cache, write_cache)
         with kernels.phase("wo"):
-            kernels.linear(att, self.w_o, self.b_o, residual, accumulate=True)
+            kernels.linear(att, self.w_o, self.b_o, residual, accumulate=accumulate)
 
     def forward_then_norm(self, ctx, xn, residual, cache, state, write_cache, norm, out):
         args = norm.fused_args()

@@ -44,11 +44,17 @@ def make_part(category: str, spec: PartSpec, **context: Any) -> "Part":
 
 @dataclass(frozen=True)
 class CacheSpec:
-    """What a mixer asks of the paged cache: per token ``2 * num_kv_heads * head_dim`` values
-    (keys then values); ``window`` = 0 keeps every key, else only the most recent ``window``."""
+    """What a mixer asks of the paged cache: per token ``num_kv_heads * (head_dim + value_dim)`` values
+    (keys then values); ``window`` = 0 keeps every key, else only the most recent ``window``;
+    ``v_head_dim`` = 0 means value heads as wide as key heads."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    v_head_dim: int = 0
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 @dataclass(frozen=True)

@@ -1,5 +1,9 @@
-"""Pre-norm residual arrangement: ``x += mixer(norm1(x)); x += ffn(norm2(x))`` (src/model.c:580-623)."""
+"""Residual arrangements.  Pre-norm: ``x += mixer(norm1(x)); x += ffn(norm2(x))`` (src/model.c:580-623).
+Norm on both sides of each sublayer: ``x += post1(mixer(norm1(x))); x += post2(ffn(norm2(x)))``, where a layer may
+have no feed-forward at all."""
 from __future__ import annotations
+
+import torch
 
 from .base import Block, register_part
 
@@ -32,4 +36,36 @@ class PreNormResidual(Block):
         return None
 
 
+class SandwichResidual(Block):
+    """``x += post1(mixer(norm1(x)))``, then, if the layer has a feed-forward, ``x += post2(ffn(norm2(x)))``.  The
+    sublayers write their output to a float32 buffer (``accumulate=False``) instead of adding it to the stream; the
+    post-norm adds it, and where it can it hands back the following norm of the new stream from the same pass."""
+    graph_safe = True
+
+    def __init__(self, **_):
+        pass
+
+    def forward(self, ctx, x, norm1, mixer, norm2, ffn, cache, state, write_cache, xn_ready=None, next_norm=None,
+                post1=None, post2=None):
+        if post1 is None or (ffn is not None and post2 is None):
+            raise ValueError("this block needs a norm behind each sublayer")
+        if xn_ready is None:
+            xn = ctx.buf("block_xn", x.shape, ctx.run_dtype)
+            norm1.forward(x, xn)
+        else:
+            xn = xn_ready
+        y = ctx.buf("block_y", x.shape, torch.float32)
+        mixer.forward(ctx, xn, y, cache, state, write_cache, accumulate=False)
+        if ffn is None:
+            nxt = ctx.buf("block_xn", x.shape, ctx.run_dtype) if next_norm is not None else None
+            return nxt if post1.add_into(y, x, next_norm, nxt) else None
+        xn2 = ctx.buf("block_xn2", x.shape, ctx.run_dtype)
+        if not post1.add_into(y, x, norm2, xn2):
+            norm2.forward(x, xn2)
+        ffn.forward(ctx, xn2, y, accumulate=False)
+        nxt = ctx.buf("block_xn", x.shape, ctx.run_dtype) if next_norm is not None else None
+        return nxt if post2.add_into(y, x, next_norm, nxt) else None
+
+
 register_part("block", "prenorm_residual", PreNormResidual)
+register_part("block", "sandwich_residual", SandwichResidual)

@@ -32,9 +32,10 @@ class Embedding(Part):
 class LinearHead(Part):
     graph_safe = True
 
-    def __init__(self, vocab_size: int, hidden_size: int, tensor: str, tied_to=None, **_):
+    def __init__(self, vocab_size: int, hidden_size: int, tensor: str, tied_to=None, scale: float = 1.0, **_):
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
         self.tensor, self.tied_to = tensor, tied_to
+        self.scale = float(scale)               # logits = (head . x) * scale
         self.weight = None
 
     def tensor_specs(self):
@@ -57,6 +58,8 @@ class LinearHead(Part):
     def forward(self, xn: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
         with kernels.phase("head"):
             kernels.linear(xn, self.weight, None, logits, accumulate=False)
+            if self.scale != 1.0:
+                kernels.scale_(logits, self.scale)
         return logits
 
 

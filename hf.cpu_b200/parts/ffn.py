@@ -1,12 +1,14 @@
-"""Dense SwiGLU feed-forward: ``h = silu(x Wg^T) * (x Wu^T)``; ``out = h Wd^T`` added to the
-residual; no biases (src/model.c:612-623, src/mathx.c:34).  Gate and up are one matrix product
-over the concatenated rows, as the reference serves both with one pass over the activations
+"""Dense gated feed-forward: ``h = act(x Wg^T) * (x Wu^T)``; ``out = h Wd^T`` added to the
+residual; no biases (src/model.c:612-623, src/mathx.c:34: ``act`` = silu, the reference's only one;
+``activation`` may also name relu or gelu_tanh).  Gate and up are one matrix product over the
+concatenated rows, as the reference serves both with one pass over the activations
 (src/model.c:612-615)."""
 from __future__ import annotations
 
 import torch
 
 from .. import kernels
+from ..config.base import UnsupportedError
 from ..weights.loader import TensorSpec, fused_rows
 from .base import FeedForward, register_part
 
@@ -14,8 +16,11 @@ from .base import FeedForward, register_part
 class SwiGlu(FeedForward):
     graph_safe = True
 
-    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str, names=None, **_):
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str, names=None, activation: str = "silu", **_):
         self.E, self.F = int(hidden_size), int(intermediate_size)
+        if activation not in ("silu", "relu", "gelu_tanh"):
+            raise UnsupportedError(f"gated feed-forward: activation '{activation}' is not supported")
+        self.activation = activation
         n = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
         n.update(names or {})
         self.names = {k: f"{prefix}.{v}" for k, v in n.items()}
@@ -41,13 +46,14 @@ class SwiGlu(FeedForward):
         gu = ctx.buf("ffn_gate_up", (T, 2 * self.F), xn.dtype)
         h = ctx.buf("ffn_h", (T, self.F), xn.dtype)
         with kernels.phase("gate_up"):
-            kernels.linear_swiglu(xn, self.w_gate_up, gu, h)
+            kernels.linear_glu(xn, self.w_gate_up, gu, h, self.activation)
         return h
 
-    def forward(self, ctx, xn, residual):
+    def forward(self, ctx, xn, residual, accumulate=True):
+        """``accumulate=False`` stores the output in ``residual`` (float32) instead of adding it."""
         h = self._hidden(ctx, xn)
         with kernels.phase("down"):
-            kernels.linear(h, self.w_down, None, residual, accumulate=True)
+            kernels.linear(h, self.w_down, None, residual, accumulate=accumulate)
 
     def forward_then_norm(self, ctx, xn, residual, norm, out):
         args = norm.fused_args()
@@ -61,3 +67,4 @@ class SwiGlu(FeedForward):
 
 
 register_part("ffn", "swiglu", SwiGlu)
+register_part("ffn", "gated", SwiGlu)               # the same part under the name that does not fix the activation

@@ -1,4 +1,6 @@
-"""RMSNorm: ``y_i = (x_i * rsqrt(mean(x^2) + eps)) * w_i`` (src/mathx.c:65-75, used at src/model.c:580, :611, :632)."""
+"""Norms.  RMSNorm: ``y_i = (x_i * rsqrt(mean(x^2) + eps)) * w_i`` (src/mathx.c:65-75, used at src/model.c:580,
+:611, :632).  Dynamic Tanh: ``y_i = tanh(alpha * x_i) * w_i + b_i`` with a learned scalar ``alpha``: element-wise,
+no mean or variance of the row is taken (the reference has no such norm)."""
 from __future__ import annotations
 
 import torch
@@ -30,4 +32,42 @@ class RmsNorm(Norm):
         return out
 
 
+class DynamicTanh(Norm):
+    """``tanh(alpha * x) * w + b``; the tensors are ``tensor`` (w), ``tensor + bias_suffix`` and ``tensor + alpha_suffix``
+    (a scalar).  Being element-wise it also serves as the norm of a sublayer's *output* (:meth:`add_into`)."""
+    graph_safe = True
+
+    def __init__(self, size: int, tensor: str, bias_suffix: str = ".b", alpha_suffix: str = ".alpha", optional: bool = False, **_):
+        self.size, self.tensor = int(size), tensor
+        self.names = (tensor + alpha_suffix, tensor, tensor + bias_suffix)
+        self.optional = bool(optional)
+        self.params = None          # (alpha, w, b)
+
+    def tensor_specs(self):
+        a, w, b = self.names
+        return [TensorSpec(w, (self.size,), init="norm", optional=self.optional),
+                TensorSpec(b, (self.size,), optional=self.optional),
+                TensorSpec(a, (), init="norm", optional=self.optional)]
+
+    def bind(self, tensors, run_dtype, device):
+        if self.optional and any(n not in tensors for n in self.names):
+            return
+        alpha, w, b = (tensors[n].contiguous() for n in self.names)
+        self.params = (alpha.reshape(1), w, b)
+
+    def forward(self, x, out, rows=None):
+        with kernels.phase("glue"):
+            kernels.dyt(x, self.params, out, rows)
+        return out
+
+    def add_into(self, y, residual, next_norm=None, out=None):
+        """residual += norm(y); when ``next_norm`` is another Dynamic Tanh, ``out = next_norm(residual)`` comes out of
+        the same pass.  Returns whether ``out`` was written."""
+        fused = out is not None and isinstance(next_norm, DynamicTanh)
+        with kernels.phase("glue"):
+            kernels.dyt_residual(y, self.params, residual, next_norm.params if fused else None, out if fused else None)
+        return fused
+
+
 register_part("norm", "rmsnorm", RmsNorm)
+register_part("norm", "dynamic_tanh", DynamicTanh)

@@ -48,13 +48,14 @@ class EmuBackend:
         kf[slots[ok].long()] = rot(x[:, H:H + G])[ok].to(k_cache.dtype)
         vf[slots[ok].long()] = x[:, H + G:][ok].to(v_cache.dtype)
 
-    def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tiles=None):
+    def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tiles=None, dv=None):
         T = q.shape[0]
         bs = meta.block_size
-        kf, vf = k_cache.view(-1, G, d).float(), v_cache.view(-1, G, d).float()
+        dv = d if dv is None else dv
+        kf, vf = k_cache.reshape(-1, G, d).float(), v_cache.reshape(-1, G, dv).float()
         seqs, poss, table = ctx.token_seq.tolist(), ctx.positions.tolist(), meta.block_table.tolist()
         qf = q.float().view(T, H, d)
-        res = torch.zeros(T, H, d, dtype=torch.float32, device=q.device)
+        res = torch.zeros(T, H, dv, dtype=torch.float32, device=q.device)
         for t in range(T):
             pos, row = poss[t], table[seqs[t]]
             lo = max(0, pos - window + 1) if window > 0 else 0
@@ -70,7 +71,7 @@ class EmuBackend:
                 s = (k[:, g] @ qf[t, h]) * scale
                 p = torch.softmax(s, 0)
                 res[t, h] = p @ v[:, g]
-        out.copy_(res.view(T, H * d).to(out.dtype))
+        out.copy_(res.view(T, H * dv).to(out.dtype))
 
     def swiglu(self, gu, out, interleaved):
         F = out.shape[1]
@@ -92,6 +93,104 @@ class EmuBackend:
     def linear_rope_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d):
         self.linear(a, w, bias, qkv_buf, False)
         self.rope_kv_write(qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d)
+
+    # ---- Dynamic Tanh norms, unit-rms heads, gated and routed feed-forwards ----
+    @staticmethod
+    def _dyt(x, p):
+        alpha, w, b = p
+        return torch.tanh(alpha.float() * x.float()) * w.float() + b.float()
+
+    def dyt(self, x, params, out, rows):
+        xr = x if rows is None else x[rows.long()]
+        out.copy_(self._dyt(xr, params).to(out.dtype))
+
+    def dyt_residual(self, y, post, residual, nxt, out):
+        residual.add_(self._dyt(y, post))
+        if nxt is not None:
+            out.copy_(self._dyt(residual, nxt).to(out.dtype))
+
+    def linear_rope_norm_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d, dv,
+                            norm_eps):
+        self.linear(a, w, bias, qkv_buf, False)
+        T = a.shape[0]
+
+        def finish(v):                                 # [T, heads, d]
+            if n_rot:
+                half = n_rot // 2
+                cs = cos_sin[positions.long()]
+                c, s = cs[:, None, :, 0], cs[:, None, :, 1]
+                x, y = v[..., :half], v[..., half:n_rot]
+                v = torch.cat([x * c - y * s, x * s + y * c, v[..., n_rot:]], -1)
+            if norm_eps is not None:
+                v = v / torch.sqrt((v * v).mean(-1, keepdim=True) + norm_eps)
+            return v
+        q_out.copy_(finish(qkv_buf[:, :H * d].view(T, H, d)).reshape(T, H * d).to(q_out.dtype))
+        if not G or slots is None:
+            return
+        ok = slots >= 0
+        k = finish(qkv_buf[:, H * d:(H + G) * d].view(T, G, d))
+        v = qkv_buf[:, (H + G) * d:].view(T, G, dv)
+        k_cache.view(-1, G, d)[slots[ok].long()] = k[ok].to(k_cache.dtype)
+        v_cache.view(-1, G, dv)[slots[ok].long()] = v[ok].to(v_cache.dtype)
+
+    @staticmethod
+    def _activate(z, act):
+        if act == 0:
+            return z / (1.0 + torch.exp(-z))
+        if act == 1:
+            return torch.relu(z)
+        if act == 2:
+            return 0.5 * z * (1.0 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+        if act == 3:
+            return torch.relu(z) ** 2
+        return z
+
+    def linear_glu(self, a, w, gu_buf, out, act):
+        self.linear(a, w, None, gu_buf, False)
+        g, u = gu_buf[:, 0::2].float(), gu_buf[:, 1::2].float()
+        out.copy_((self._activate(g, act) * u).to(out.dtype))
+
+    def linear_act(self, a, w, out, act):
+        out.copy_(self._activate(a.float() @ w.float().T, act).to(out.dtype))
+
+    def scale_(self, x, s):
+        x.mul_(s)
+
+    def moe_route(self, h, w, b, top, ids, weights):
+        z = h.float() @ w.float().T
+        if b is not None:
+            z = z + b.float()
+        zc, idx = torch.sort(z, dim=-1, descending=True, stable=True)
+        ids.copy_(idx[:, :top].int())
+        weights.copy_(torch.softmax(zc[:, :top], -1))
+
+    def moe_group(self, ids, experts, order, tile_expert, tile_p0, tile_n, n_tiles):
+        from hfcpu_b200.kernels import MOE_TILE
+        flat = ids.reshape(-1)
+        srt = torch.sort(flat, stable=True).indices.int()
+        order[:flat.numel()] = srt
+        counts = torch.bincount(flat.long(), minlength=experts).tolist()
+        n = at = 0
+        for e, c in enumerate(counts):
+            for p0 in range(0, c, MOE_TILE):
+                tile_expert[n], tile_p0[n], tile_n[n] = e, at + p0, min(MOE_TILE, c - p0)
+                n += 1
+            at += c
+        n_tiles[0] = n
+
+    def moe_gemm(self, a, w, out, act, order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles, max_tiles):
+        assert int(n_tiles[0]) <= max_tiles
+        for i in range(int(n_tiles[0])):
+            e, p0, n = int(tile_expert[i]), int(tile_p0[i]), int(tile_n[i])
+            places = torch.arange(p0, p0 + n)
+            pairs = order[places].long()
+            src = pairs // src_div if src_div else places
+            dst = pairs if scatter else places
+            out[dst] = self._activate(a[src].float() @ w[e].float().T, act).to(out.dtype)
+
+    def moe_combine(self, y, weights, out):
+        T, top = weights.shape
+        out.copy_((weights[:, :, None] * y.float().view(T, top, -1)).sum(1))
 
     def argmax(self, logits, out):
         out.copy_(torch.argmax(logits, dim=-1).int())
