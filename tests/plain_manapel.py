@@ -54,8 +54,11 @@ def unit_rms(x, eps):
     return x / np.sqrt((x * x).mean(-1, keepdims=True) + eps)
 
 
-def rotate_half(x, positions, dims, base):
+def rotate_half(x, positions, rot):
     """x [T, heads, dim]: dimension i < dims/2 pairs with i + dims/2; angle = position * base^(-2i/dims)."""
+    if not rot or not rot["dims"]:
+        return x
+    dims, base = rot["dims"], rot["base"]
     half = dims // 2
     f = base ** (-2.0 * np.arange(half) / dims)
     a = np.asarray(positions, dtype=np.float64)[:, None, None] * f[None, None, :]
@@ -69,7 +72,7 @@ def keys_values(h, W, p, m, eps):
     G, d, dv = m["kv_heads"], m["dim"], m["vdim"]
     k = (h @ W[p + ".mix.k"].T + W[p + ".mix.k.b"]).reshape(T, G, d)
     v = (h @ W[p + ".mix.v"].T + W[p + ".mix.v.b"]).reshape(T, G, dv)
-    k = unit_rms(rotate_half(k, np.arange(T), m["rot"]["dims"], m["rot"]["base"]), eps)
+    k = unit_rms(rotate_half(k, np.arange(T), m.get("rot")), eps)
     return k, v
 
 
@@ -78,7 +81,7 @@ def attention(h, W, p, m, eps, kv):
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = (h @ W[p + ".mix.q"].T + W[p + ".mix.q.b"]).reshape(T, H, d)
-    q = unit_rms(rotate_half(q, np.arange(T), m["rot"]["dims"], m["rot"]["base"]), eps)
+    q = unit_rms(rotate_half(q, np.arange(T), m.get("rot")), eps)
     k, v = kv
     out = np.zeros((T, H, dv))
     mask = np.tril(np.ones((T, T), dtype=bool))
@@ -145,3 +148,11 @@ def forward(cfg, W, ids, layers_out=None):
         if layers_out is not None:
             layers_out.append(x.copy())
     return (dynamic_tanh(x, W, "final.norm") @ W["head"].T) * cfg["logit_scale"]
+
+
+def greedy(cfg, W, prompt, n_new):
+    ids, out = list(prompt), []
+    for _ in range(n_new):
+        out.append(int(np.argmax(forward(cfg, W, ids)[-1])))
+        ids.append(out[-1])
+    return out
