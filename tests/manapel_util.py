@@ -52,23 +52,25 @@ BLOCKS = {"odd": 8, "wide": 16, "thin": 4}
 
 
 def make_folder(cfg_dict, folder, seed, dtype=torch.float32, edit=None):
-    """A model folder whose values leave the linear part of tanh, with routers that decide clearly."""
+    """A model folder whose values leave the linear part of tanh, with routers that decide clearly.  Stored in bfloat16
+    the weights are smaller, so that the rounding of large intermediate values does not swamp the comparison."""
     from hfcpu_b200.config import config_from_dict
     from hfcpu_b200.models import build_model_specs
     from hfcpu_b200.weights import random_tensors, write_safetensors, weights_path
     cfg = config_from_dict(cfg_dict)
     cfg.save(folder)
-    tensors = random_tensors(build_model_specs(cfg), seed, torch.float32, std=0.08)
+    soft = dtype == torch.bfloat16
+    tensors = random_tensors(build_model_specs(cfg), seed, torch.float32, std=0.04 if soft else 0.08)
     g = torch.Generator().manual_seed(seed)
     for name in tensors:
         if name == "embed":
-            tensors[name] = tensors[name] * 12
+            tensors[name] = tensors[name] * (10 if soft else 12)
         elif name.endswith(".alpha"):
             tensors[name] = torch.empty(()).uniform_(0.4, 1.6, generator=g)
         elif name.endswith(".router"):
             tensors[name] = tensors[name] * 6
         elif ".mix.o" in name or name.endswith(".down"):
-            tensors[name] = tensors[name] * 4
+            tensors[name] = tensors[name] * 2
     if edit:
         edit(tensors)
     # what is stored is what both sides read: round once to the storage type
