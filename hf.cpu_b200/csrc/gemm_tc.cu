@@ -54,6 +54,8 @@ struct GemmParams {
     void *out; int out_dt;             // [M, N]
     const void *bias; int bias_dt;     // [N] or null
     int mode;
+    int act;                           // EPI_SWIGLU: the gate's activation (0 silu, else an HFB_ACT_* code);
+                                       // EPI_STORE: 0 none, else the HFB_ACT_* code applied to sum + bias
     float *partial;                    // [splits, M, N] when mode == EPI_PARTIAL
     // mode == EPI_ROPE_KV (pair kernel, tiles of whole heads): the output is the q|k|v row of a token; bias, rounding
     // to bfloat16, rotation of the query and key heads by the token's position, queries to q_out, keys and values to
@@ -90,6 +92,15 @@ template <int BN, int STAGES> constexpr uint32_t gemm_smem_bytes()
     return 1024 + STAGES * (X_BYTES + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16;
 }
 
+// The activations an epilogue may apply (codes of hfb200.h; 0 = silu, and in EPI_STORE "none").
+__device__ __forceinline__ float epi_act(float z, int act)
+{
+    if (act == HFB_ACT_RELU) return fmaxf(z, 0.f);
+    if (act == HFB_ACT_RELU2) { const float r = fmaxf(z, 0.f); return r * r; }
+    if (act == HFB_ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return z / (1.0f + expf(-z));
+}
+
 // One chunk of 16 accumulator columns of one row: v[i] is element (xr, y0 + i) of X . Y^T.
 // `live` false: the same instructions, nothing stored (the few-token form runs its epilogue once this way while the
 // first weights are on their way, so that its code is in the instruction cache when the first tile is done: fetched
@@ -113,7 +124,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32
             const float their_first = __shfl_xor_sync(0xffffffffu, first, 1);
             const float their_second = __shfl_xor_sync(0xffffffffu, second, 1);
             const float g = odd ? their_second : first, u = odd ? second : their_first;
-            const float h = (g / (1.0f + expf(-g))) * u;
+            const float h = epi_act(g, p.act) * u;
             const int i = 2 * j + odd;
             if (i < n_tok) {
                 if (p.out_dt == HFB_BF16) ((__nv_bfloat16 *)p.out)[at + (size_t)i * half_n] = __float2bfloat16_rn(h);
@@ -142,6 +153,12 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32
                         if (i >= n_tok) break;
                         dst[(size_t)i * p.N] += __uint_as_float(v[i]) + b;
                     }
+                } else if (p.act) {
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        if (i >= n_tok) break;
+                        store_any(p.out, p.out_dt, at + (size_t)i * p.N, epi_act(__uint_as_float(v[i]) + b, p.act));
+                    }
                 } else if (p.out_dt == HFB_BF16) {
                     __nv_bfloat16 *dst = (__nv_bfloat16 *)p.out + at;
 #pragma unroll
@@ -166,7 +183,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 float g = __uint_as_float(v[2 * i]), u = __uint_as_float(v[2 * i + 1]);
-                h[i] = (g / (1.0f + expf(-g))) * u;
+                h[i] = epi_act(g, p.act) * u;
             }
             size_t o = (size_t)xr * (p.N >> 1) + (y0 >> 1);
             if (y0 + 16 <= p.N && (p.N & 15) == 0 && p.out_dt == HFB_BF16) {
@@ -201,6 +218,10 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32
                 for (int i = 0; i < 16; i++)
                     if (full || y0 + i < p.N) f[i] += load_any(p.bias, p.bias_dt, y0 + i);
             }
+        }
+        if (p.mode == EPI_STORE && p.act) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) f[i] = epi_act(f[i], p.act);
         }
         if (p.mode == EPI_PARTIAL) {
             float *dst = p.partial + (size_t)split * p.M * p.N + o;
@@ -1058,6 +1079,36 @@ extern "C" int hfb_linear_tc_swiglu(const void *a, const void *w, void *out, int
     int bn;
     if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my)) != HFB_OK) return rc;
     p.out = out; p.out_dt = out_dt; p.bias = nullptr; p.mode = EPI_SWIGLU;
+    return launch_bn(bn, mx, my, p, (cudaStream_t)s);
+}
+
+// The gated form with another activation of the gate than silu (an HFB_ACT_* code).
+extern "C" int hfb_linear_tc_glu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, int act, hfb_stream s)
+{
+    if (M <= 0 || N <= 0) return HFB_OK;
+    int rc = check_tc_args("linear_tc_glu", a, w, out, M, N, K);
+    if (rc != HFB_OK) return rc;
+    if ((N & 1) || !valid_dt(out_dt) || act < 0 || act >= HFB_ACT_NONE) return fail(HFB_EINVAL, "linear_tc_glu: bad arguments");
+    GemmParams p{};
+    CUtensorMap mx, my;
+    int bn;
+    if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my)) != HFB_OK) return rc;
+    p.out = out; p.out_dt = out_dt; p.bias = nullptr; p.mode = EPI_SWIGLU; p.act = act;
+    return launch_bn(bn, mx, my, p, (cudaStream_t)s);
+}
+
+// out = act(a . w^T) with the activation (an HFB_ACT_* code other than silu) in the product's epilogue; K is not split.
+extern "C" int hfb_linear_tc_act(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, int act, hfb_stream s)
+{
+    if (M <= 0 || N <= 0) return HFB_OK;
+    int rc = check_tc_args("linear_tc_act", a, w, out, M, N, K);
+    if (rc != HFB_OK) return rc;
+    if (!valid_dt(out_dt) || act <= 0 || act >= HFB_ACT_NONE) return fail(HFB_EINVAL, "linear_tc_act: bad arguments");
+    GemmParams p{};
+    CUtensorMap mx, my;
+    int bn;
+    if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my)) != HFB_OK) return rc;
+    p.out = out; p.out_dt = out_dt; p.bias = nullptr; p.mode = EPI_STORE; p.act = act;
     return launch_bn(bn, mx, my, p, (cudaStream_t)s);
 }
 

@@ -53,6 +53,11 @@ int hfb_linear_tc(const void *a, const void *w, const void *bias, int bias_dt, v
 /* The product with a SwiGLU epilogue: w holds gate row i at 2i and up row i at 2i+1; out[M, N/2]. */
 int hfb_linear_tc_swiglu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, hfb_stream s);
 
+/* The gated product with another activation of the gate (HFB_ACT_* code), and out = act(a . w^T) with the activation in
+ * the epilogue (act other than silu; K is never split). */
+int hfb_linear_tc_glu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, int act, hfb_stream s);
+int hfb_linear_tc_act(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, int act, hfb_stream s);
+
 /* q|k|v of 256 tokens and more with the rest of the step in the product's epilogue: bias, rounding to bfloat16,
  * rotation of the query and key heads by cos_sin [n_positions, d / 2, 2] at the tokens' positions, queries to q_out
  * [M, H d], keys and values to cache slot slots[t] (null: nothing is cached).  bfloat16 throughout, head sizes 64 and

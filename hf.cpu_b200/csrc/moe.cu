@@ -7,6 +7,8 @@
 // over k, and a token's choices are summed in the order the router made them: what a token gets does not depend on
 // which other tokens are in the step nor on the order of the lists.
 #include "common.cuh"
+#include <stdlib.h>
+#include <string.h>
 
 static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
 
@@ -177,6 +179,116 @@ moe_gemm_kernel(const TA *__restrict__ a, const TW *__restrict__ w, void *out, i
     }
 }
 
+// The same grouped product for bfloat16 operands on the tensor cores (mma.sync m16n8k16, float32 accumulators): four
+// warps, each 16 places x 64 features of the tile; operands go through registers into padded shared memory, 32 of k
+// at a time, the next piece on its way while the current one is multiplied.  K is a multiple of 8 and the operands are
+// 16-byte aligned (every 16-byte piece of a row lies wholly inside or outside K).
+constexpr int MK = 32, MPAD = 8;
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(128)
+moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__restrict__ w, void *out, int out_dt, int act,
+                    int N, int K, const int32_t *order, int src_div, int scatter, const int32_t *tile_expert,
+                    const int32_t *tile_p0, const int32_t *tile_n, const int32_t *n_tiles)
+{
+    pdl_sync();
+    const int ti = blockIdx.y;
+    if (ti >= *n_tiles) return;
+    __shared__ __align__(16) __nv_bfloat16 sa[GT][MK + MPAD];
+    __shared__ __align__(16) __nv_bfloat16 sw[GT][MK + MPAD];
+    __shared__ int s_src[GT], s_dst[GT];
+    const int e = tile_expert[ti], p0 = tile_p0[ti], rows = tile_n[ti];
+    const int n0 = blockIdx.x * GT;
+    if (threadIdx.x < GT) {
+        const int r = threadIdx.x;
+        int src = -1, dst = -1;
+        if (r < rows) {
+            const int p = p0 + r, pair = order[p];
+            src = src_div > 0 ? pair / src_div : p;
+            dst = scatter ? pair : p;
+        }
+        s_src[r] = src;
+        s_dst[r] = dst;
+    }
+    __syncthreads();
+    const __nv_bfloat16 *we = w + (size_t)e * N * K;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    // the two 16-byte pieces of each operand this thread moves per 32 of k
+    const int vrow[2] = {(int)threadIdx.x / 4, (int)threadIdx.x / 4 + 32}, vk = (threadIdx.x & 3) * 8;
+    const __nv_bfloat16 *pa[2], *pw[2];
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const int src = s_src[vrow[i]], gn = n0 + vrow[i];
+        pa[i] = src >= 0 ? a + (size_t)src * K + vk : nullptr;
+        pw[i] = gn < N ? we + (size_t)gn * K + vk : nullptr;
+    }
+    uint4 ra[2], rw[2];
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const bool in = k0 + vk < K;
+            ra[i] = (pa[i] && in) ? *(const uint4 *)(pa[i] + k0) : zero;
+            rw[i] = (pw[i] && in) ? *(const uint4 *)(pw[i] + k0) : zero;
+        }
+    };
+    float acc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+    fetch(0);
+    for (int k0 = 0; k0 < K; k0 += MK) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            *(uint4 *)&sa[vrow[i]][vk] = ra[i];
+            *(uint4 *)&sw[vrow[i]][vk] = rw[i];
+        }
+        __syncthreads();
+        if (k0 + MK < K) fetch(k0 + MK);
+#pragma unroll
+        for (int ks = 0; ks < MK; ks += 16) {
+            uint32_t af[4];
+            af[0] = *(const uint32_t *)&sa[16 * warp + g][ks + 2 * t];
+            af[1] = *(const uint32_t *)&sa[16 * warp + g + 8][ks + 2 * t];
+            af[2] = *(const uint32_t *)&sa[16 * warp + g][ks + 2 * t + 8];
+            af[3] = *(const uint32_t *)&sa[16 * warp + g + 8][ks + 2 * t + 8];
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++) {
+                const uint32_t b0 = *(const uint32_t *)&sw[nt * 8 + g][ks + 2 * t];
+                const uint32_t b1 = *(const uint32_t *)&sw[nt * 8 + g][ks + 2 * t + 8];
+                mma_bf16(acc[nt], af, b0, b1);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        const int dst = s_dst[16 * warp + g + 8 * half];
+        if (dst < 0) continue;
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) {
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int gn = n0 + nt * 8 + 2 * t + j;
+                if (gn >= N) continue;
+                float v = acc[nt][2 * half + j];
+                if (act == HFB_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
+                else if (act == HFB_ACT_RELU) v = fmaxf(v, 0.f);
+                else if (act == HFB_ACT_SILU) v = v / (1.0f + expf(-v));
+                else if (act == HFB_ACT_GELU_TANH) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+                store_any(out, out_dt, (size_t)dst * N + gn, v);
+            }
+        }
+    }
+}
+
 template <typename TY>
 __global__ void moe_combine_kernel(const TY *y, const float *weights, float *out, int T, int top, int N)
 {
@@ -195,6 +307,13 @@ __global__ void moe_combine_kernel(const TY *y, const float *weights, float *out
 }  // namespace hfb
 
 using namespace hfb;
+
+// HFB_GEMM=plain in the environment keeps the grouped products on the float32 multiply-add kernel, as it does the others.
+static bool plain_products()
+{
+    static const int v = [] { const char *e = getenv("HFB_GEMM"); return e && strcmp(e, "plain") == 0 ? 1 : 0; }();
+    return v != 0;
+}
 
 extern "C" int hfb_moe_route(const void *h, int h_dt, const void *w, const void *b, int w_dt, int T, int K, int E, int top,
                              int32_t *ids, float *weights, hfb_stream s)
@@ -242,6 +361,12 @@ extern "C" int hfb_moe_gemm(const void *a, int a_dt, const void *w, int w_dt, vo
     if (max_tiles > 65535) return fail(HFB_ENOTSUP, "moe_gemm: %d tiles exceed the grid", max_tiles);
     const dim3 grid((N + GT - 1) / GT, max_tiles);
     cudaStream_t st = (cudaStream_t)s;
+    if (a_dt == HFB_BF16 && w_dt == HFB_BF16 && (K & 7) == 0 && ((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0 &&
+        !plain_products()) {
+        g_launch_err = launch_pdl(moe_gemm_mma_kernel, grid, dim3(128), 0, st, (const __nv_bfloat16 *)a, (const __nv_bfloat16 *)w, out, out_dt, act, N, K,
+                                  order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles);
+        return check_pdl_launch(g_launch_err, "moe_gemm_mma");
+    }
 #define LAUNCH(TA, TW) g_launch_err = launch_pdl(moe_gemm_kernel<TA, TW>, grid, dim3(256), 0, st, (const TA *)a, (const TW *)w, out, out_dt, act, N, K, order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles)
     if (a_dt == HFB_F32 && w_dt == HFB_F32) LAUNCH(float, float);
     else if (a_dt == HFB_F32) LAUNCH(float, __nv_bfloat16);

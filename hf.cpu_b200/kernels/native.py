@@ -367,6 +367,11 @@ class NativeBackend:
 
     def linear_glu(self, a, w, gu_buf, out, act):
         self._on_gpu(a, w, gu_buf, out)
+        if self._tc_ok(a, w, out):
+            M, K = a.shape
+            self._check(self.lib.hfb_linear_tc_glu(_p(a), _p(w), _p(out), c_int(_dt(out)), c_int(M), c_int(w.shape[0]), c_int(K),
+                                                   c_int(act), self._stream()), "linear_tc_glu")
+            return
         self.linear(a, w, None, gu_buf, False)
         T, F = out.shape
         self._check(self.lib.hfb_glu(_p(gu_buf), _p(out), c_int(_dt(out)), c_int(T), c_int(F), c_int(1), c_int(act),
@@ -374,6 +379,11 @@ class NativeBackend:
 
     def linear_act(self, a, w, out, act):
         self._on_gpu(a, w, out)
+        if self._tc_ok(a, w, out) and 0 < act < 4:
+            M, K = a.shape
+            self._check(self.lib.hfb_linear_tc_act(_p(a), _p(w), _p(out), c_int(_dt(out)), c_int(M), c_int(w.shape[0]), c_int(K),
+                                                   c_int(act), self._stream()), "linear_tc_act")
+            return
         self.linear(a, w, None, out, False)
         self._check(self.lib.hfb_act(_p(out), _p(out), c_int(_dt(out)), c_int64(out.numel()), c_int(act), self._stream()), "act")
 
