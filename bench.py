@@ -223,6 +223,134 @@ def run_workload(args):
     return 0
 
 
+# ---- `--compare manapel`: the Manapel design beside the Qwen2 decoder at equal layer sizes ---------------------------
+# Sizes that resemble real layers.  The Qwen2 twin has the same width, heads and vocabulary and a gated feed-forward
+# with as many weights per token as the routed layer's chosen experts plus its shared one (3 F' E = 2 (top F + Fs) E).
+COMPARE_SIZES = {
+    "w1024_h64": dict(width=1024, heads=16, kv=4, dim=64, rot=32, experts=16, top=2, ff=512, shared=1024, layers=8, vocab=32768),
+    "w2048_h128": dict(width=2048, heads=16, kv=4, dim=128, rot=64, experts=32, top=4, ff=1024, shared=2048, layers=8, vocab=32768),
+    "w4096_h128": dict(width=4096, heads=32, kv=8, dim=128, rot=128, experts=32, top=4, ff=2048, shared=4096, layers=4, vocab=32768),
+}
+
+
+def compare_configs(z):
+    att = lambda src=None: dict(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5,
+                                rot=dict(dims=z["rot"], base=10000.0), **({"kv_from": src} if src is not None else {}))
+    moe = dict(kind="moe", router=dict(experts=z["experts"], top=z["top"]), expert=dict(ff=z["ff"]), shared=dict(ff=z["shared"]))
+    per_token = 2 * (z["top"] * z["ff"] + z["shared"])
+    dense = (per_token // 3 + 7) // 8 * 8
+    layers = []
+    for i in range(z["layers"]):          # the first layer dense, every second layer on its neighbour's keys and values
+        layers.append(dict(type="attention", mixer=att(i - 1 if i % 2 else None), mlp=dict(kind="dense", ff=dense) if i == 0 else moe))
+    manapel = dict(architecture="Manapel", vocab=z["vocab"], width=z["width"], logit_scale=1.0, norm=dict(eps=1e-5), layers=layers,
+                   max_positions=8192)
+    qwen = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=z["layers"], hidden_size=z["width"],
+                num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["dim"], intermediate_size=dense,
+                vocab_size=z["vocab"], max_position_embeddings=8192, rms_norm_eps=1e-6, rope_theta=1e4, tie_word_embeddings=False)
+    return manapel, qwen
+
+
+def phase_work(model, q_len, ctx_len, batch):
+    """Per phase of the forward pass: (operations, bytes that must move) of one step of ``batch`` requests that bring
+    ``q_len`` tokens each and hold ``ctx_len`` afterwards, summed over the layers: what the roofline of each phase's
+    kernels is made of.  Weights are read once a step; a routed layer reads the experts its tokens choose (at most all)."""
+    T = batch * q_len
+    el = 2
+    work = {k: [0.0, 0.0] for k in ("qkv", "attn", "wo", "gate_up", "down", "head")}
+
+    def add(k, ops, nbytes):
+        work[k][0] += ops
+        work[k][1] += nbytes
+    for e in model.plan.schedule:
+        L = model.layers[e.layer]
+        m, f = L.mixer, L.ffn
+        dv = getattr(m, "dv", m.d)
+        add("qkv", 2.0 * T * m.w_qkv.numel(), el * (m.w_qkv.numel() + T * (m.E + m.w_qkv.shape[0])))
+        add("wo", 2.0 * T * m.w_o.numel(), el * (m.w_o.numel() + T * m.H * dv) + 4 * T * m.E)
+        pairs = batch * (q_len * (ctx_len - q_len) + q_len * (q_len + 1) // 2)
+        add("attn", 2.0 * m.H * (m.d + dv) * pairs, el * (batch * ctx_len * m.G * (m.d + dv) + 2 * T * m.H * m.d))
+        if hasattr(f, "w_gate_up"):
+            add("gate_up", 2.0 * T * f.w_gate_up.numel(), el * (f.w_gate_up.numel() + T * (f.E + f.F)))
+            add("down", 2.0 * T * f.w_down.numel(), el * (f.w_down.numel() + T * f.F) + 4 * T * f.E)
+        elif f is not None:
+            used = min(f.n, T * f.top)
+            add("gate_up", 2.0 * T * f.E * (f.top * f.F + f.FS), el * (f.E * (used * f.F + f.FS) + T * (f.E + f.top * f.F + f.FS)))
+            add("down", 2.0 * T * f.E * (f.top * f.F + f.FS), el * (f.E * (used * f.F + f.FS) + T * (f.top * f.F + f.FS)) + 4 * T * f.E * (f.top + 1))
+    return work
+
+
+def run_compare(args):
+    """Prefill (one prompt) and decode (a batch of single tokens) of the Manapel design and its Qwen2 twin at each size:
+    tokens a second, and per phase of the forward pass the device time (CUDA events around the phase's kernels, steps run
+    kernel by kernel) with its share of the measured peak, the better of the operations and the bytes the phase needs."""
+    import torch
+    import hfcpu_b200
+    from hfcpu_b200 import StepEntry, kernels
+    from hfcpu_b200.config import config_from_dict
+    from hfcpu_b200.engine import measure
+    peaks, peaks_kind = measure.load_peaks(ROOT)
+    names = [n for n in COMPARE_SIZES if not args.sizes or n in args.sizes.split(",")]
+    P, B = args.prompt, args.batch
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda:0")
+    for name in names:
+        for arch, cfg_d in zip(("manapel", "qwen2"), compare_configs(COMPARE_SIZES[name])):
+            cfg = config_from_dict(cfg_d)
+            model = hfcpu_b200.random_model(cfg, seed=1, dtype=torch.bfloat16, device="cuda:0", std=0.02)
+            eng = hfcpu_b200.Engine(model, block_size=BLOCK, max_tokens=(B + 1) * (P + 64), max_requests=B + 1, ctx_max=P + 64)
+            V = model.plan.vocab_size
+            prompts = synthetic_prompts(B + 1, P, V, 3)
+            out = {"compare": name, "arch": arch, "dtype": "bf16", "data": "synthetic", "prompt": P, "batch": B,
+                   "layers": len(model.plan.schedule), "peaks": peaks_kind, "weights_gb": round(sum(p.weight_bytes() for l in model.layers for p in l.parts()) / 1e9, 3)}
+
+            def timed(fn, reps, profile):
+                for _ in range(3):
+                    fn()
+                kernels.profile.enable(profile)
+                times = []
+                for _ in range(reps):
+                    flush.zero_()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    fn()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    times.append(e0.elapsed_time(e1))
+                phases = kernels.profile.take() if profile else None
+                kernels.profile.enable(False)
+                return statistics.median(times), ({k: v / reps for k, v in phases.items() if v} if phases else None)
+
+            def prefill():
+                eng.add_request("p")
+                eng.step([StepEntry("p", prompts[B], [P - 1])])
+                eng.finish_request("p")
+            for b in range(B):
+                eng.add_request(b)
+                eng.step([StepEntry(b, prompts[b], [P - 1])])
+            held = [P]
+
+            def decode():
+                eng.step([StepEntry(b, [7], [0]) for b in range(B)])
+                held[0] += 1
+            for kind, fn, q_len, batch in (("prefill", prefill, P, 1), ("decode", decode, 1, B)):
+                ms, _ = timed(fn, args.steps if kind == "decode" else 5, False)
+                _, phases = timed(fn, 5, True)
+                work = phase_work(model, q_len, P if kind == "prefill" else held[0], batch)
+                rows = {}
+                for k, t in phases.items():
+                    if k in work and work[k][0]:
+                        ops, nbytes = work[k]
+                        rows[k] = {"us": round(t * 1e3, 1), "mma_frac": round(ops / (t * 1e-3) / (peaks["bf16_tflops"] * 1e12), 3),
+                                   "hbm_frac": round(nbytes / (t * 1e-3) / (peaks["hbm_gbs"] * 1e9), 3)}
+                    else:
+                        rows[k] = {"us": round(t * 1e3, 1)}
+                out[kind] = {"ms": round(ms, 3), "tok_s": round(batch * q_len / (ms * 1e-3), 1), "phases": rows}
+            kernels.check_device_errors()
+            print(json.dumps(out), flush=True)
+            del eng, model
+            torch.cuda.empty_cache()
+    return 0
+
+
 def synthetic_prompts(batch, n, vocab, seed):
     import torch
     g = torch.Generator().manual_seed(seed)
@@ -330,6 +458,9 @@ def main():
     ap.add_argument("--marks", action="store_true", help="with --timeline: every logged mark, not one row per kernel")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), help="run one of the other sized workloads end to end through "
                     "Session.generate instead of the record (c3: 0.5B sizes, mixed chunked prompts and decodes; c4: 32B sizes)")
+    ap.add_argument("--compare", choices=["manapel"], help="instead of the record: prefill and decode of that design beside the "
+                    "Qwen2 decoder at equal layer sizes (random weights), one JSON line per size and architecture")
+    ap.add_argument("--sizes", default="", help="with --compare: the sizes to run, with commas (default: all)")
     ap.add_argument("--ref-layers", type=int, default=28, help="layers the reference arm runs (it is a CPU program)")
     ap.add_argument("--ref-timeout", type=int, default=1500, help="seconds the reference arm may take")
     args = ap.parse_args()
@@ -344,6 +475,8 @@ def main():
         return 2
     if args.workload:
         return run_workload(args)
+    if args.compare:
+        return run_compare(args)
     warmup = max(args.warmup, 3)
 
     import torch

@@ -319,6 +319,8 @@ def planted(cfg, dtype, tmp, seed):
         W["l0.norm1"][0], W["l0.norm1.b"][0] = 1.0, 0.0
         for t, heads in (("q", m["heads"]), ("k", m["kv_heads"])):
             W[f"l0.mix.{t}"].view(heads, m["dim"], -1)[:, nr:, 0] = 25.0
+        W["l0.mix.v"] *= 8                                 # what the found key carries weighs in the output
+        W["l0.mix.o"] *= 4
     return make_folder(cfg, str(tmp), seed, DT[dtype], edit=edit)
 
 
@@ -333,7 +335,7 @@ def test_planted_far_key_at_page_borders(folders, tmp_path, name, dtype):
     n = 300
     base = [int(t) for t in requests(cfg["vocab"], [n], seed=4)["r0"]]
     base = [t if t != 7 else 8 for t in base]
-    tol = TOL[dtype] if dtype == "float32" else 5e-2
+    tol = TOL[dtype]
     for far in (0, 1, bs - 1, bs, bs + 1, 2 * bs - 1, 5 * bs, n - 2 * bs - 1):
         ids = list(base)
         ids[far] = ids[-1] = 7
@@ -342,7 +344,9 @@ def test_planted_far_key_at_page_borders(folders, tmp_path, name, dtype):
         without[far] = 8
         miss = plain.forward(C, W, without)[-1]
         matters = np.abs(want - miss).max() / np.abs(want).max()
-        assert matters > 3 * tol, f"the planted key does not matter enough ({matters:.3g})"
+        assert matters > (0.05 if dtype == "bfloat16" else 10 * tol), f"the planted key does not matter enough ({matters:.3g})"
+        if dtype == "bfloat16":
+            tol = 0.3 * matters                            # far closer to the right answer than to the one without the key
         for tail in (5, 1):
             eng = engine_for(folder, name, dtype, 320, max_requests=1)
             eng.add_request("a")
