@@ -173,10 +173,9 @@ int hfb_rope_norm_kv_write(const float *src, int splits, const void *bias, int b
                            void *q_out, void *k_cache, void *v_cache, int out_dt, int64_t cache_slots, int T,
                            int H, int G, int d, int dv, int norm, float eps, hfb_stream s);
 
-/* Router of a mixture of experts: z = h . w^T + b in float32; the `top` largest (lowest index first among equals)
- * go to ids [T, top], their softmax over the chosen logits only to weights [T, top]. */
-int hfb_moe_route(const void *h, int h_dt, const void *w, const void *b, int w_dt, int T, int K, int E, int top,
-                  int32_t *ids, float *weights, hfb_stream s);
+/* The choice of a mixture of experts' router from its float32 logits z [T, E]: the `top` largest (lowest index first
+ * among equals) go to ids [T, top], their softmax over the chosen logits only to weights [T, top]. */
+int hfb_moe_topk(const float *z, int T, int E, int top, int32_t *ids, float *weights, hfb_stream s);
 
 /* Groups the T * top (token, choice) pairs by expert: order[p] = pair at sorted place p; tiles of at most `tile`
  * places of one expert in tile_expert / tile_p0 / tile_n (room for hfb_moe_max_tiles entries); *n_tiles on the device. */

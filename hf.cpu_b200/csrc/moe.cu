@@ -16,10 +16,10 @@ namespace hfb {
 
 constexpr int ROUTE_WARPS = 4;
 
-// One warp per token.  smem per warp: E logits, then `top` chosen logits.
-template <typename TH, typename TW>
+// The choice of experts from finished router logits z [T, E] (float32): one warp per token; the `top` largest, the
+// lower index among equals; weights = softmax over the chosen logits only.  smem per warp: E logits, `top` chosen.
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
-moe_route_kernel(const TH *h, const TW *w, const TW *b, int T, int K, int E, int top, int32_t *ids, float *weights)
+moe_topk_kernel(const float *zs, int T, int E, int top, int32_t *ids, float *weights)
 {
     pdl_entry();
     pdl_sync_small();
@@ -28,14 +28,7 @@ moe_route_kernel(const TH *h, const TW *w, const TW *b, int T, int K, int E, int
     const int t = blockIdx.x * ROUTE_WARPS + warp;
     if (t >= T) return;
     float *z = route_smem + (size_t)warp * (E + top), *zc = z + E;
-    const TH *x = h + (size_t)t * K;
-    for (int e = 0; e < E; e++) {
-        const TW *wr = w + (size_t)e * K;
-        float acc = 0.f;
-        for (int k = lane; k < K; k += 32) acc = fmaf(to_f32(x[k]), to_f32(wr[k]), acc);
-        acc = warp_sum(acc);
-        if (lane == 0) z[e] = acc + (b ? to_f32(b[e]) : 0.f);
-    }
+    for (int e = lane; e < E; e += 32) z[e] = zs[(size_t)t * E + e];
     __syncwarp();
     for (int j = 0; j < top; j++) {
         float best = -INFINITY;
@@ -114,7 +107,9 @@ moe_gemm_kernel(const TA *__restrict__ a, const TW *__restrict__ w, void *out, i
     __shared__ float sa[GK][GT + 1];
     __shared__ float sw[GK][GT + 1];
     __shared__ int s_src[GT], s_dst[GT];
-    const int e = tile_expert[ti], p0 = tile_p0[ti], rows = tile_n[ti];
+    // (a tile of the lists holds up to 128 places: this kernel takes them as two halves of 64, blockIdx.z)
+    const int e = tile_expert[ti], p0 = tile_p0[ti] + GT * blockIdx.z, rows = tile_n[ti] - GT * (int)blockIdx.z;
+    if (rows <= 0) return;
     const int n0 = blockIdx.x * GT;
     if (threadIdx.x < GT) {
         const int r = threadIdx.x;
@@ -179,17 +174,26 @@ moe_gemm_kernel(const TA *__restrict__ a, const TW *__restrict__ w, void *out, i
     }
 }
 
-// The same grouped product for bfloat16 operands on the tensor cores (mma.sync m16n8k16, float32 accumulators): four
-// warps, each 16 places x 64 features of the tile; operands go through registers into padded shared memory, 32 of k
-// at a time, the next piece on its way while the current one is multiplied.  K is a multiple of 8 and the operands are
-// 16-byte aligned (every 16-byte piece of a row lies wholly inside or outside K).
-constexpr int MK = 32, MPAD = 8;
+// The same grouped product for bfloat16 operands on the tensor cores (mma.sync m16n8k16, float32 accumulators): a tile
+// of 128 places x 64 features, four warps of 32 places each; operands go through registers into padded shared memory,
+// 32 of k at a time, the next piece on its way while the current one is multiplied; fragments come out of shared
+// memory with ldmatrix.x4.  A warp whose places lie beyond the tile's count multiplies nothing (a step of single
+// tokens has a handful of places per expert).  K is a multiple of 8 and the operands are 16-byte aligned (every
+// 16-byte piece of a row lies wholly inside or outside K).
+constexpr int MT = 128, MK = 32, MPAD = 8;
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
 {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *p)
+{
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
 __global__ void __launch_bounds__(128)
@@ -200,12 +204,12 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
     pdl_sync();
     const int ti = blockIdx.y;
     if (ti >= *n_tiles) return;
-    __shared__ __align__(16) __nv_bfloat16 sa[GT][MK + MPAD];
+    __shared__ __align__(16) __nv_bfloat16 sa[MT][MK + MPAD];
     __shared__ __align__(16) __nv_bfloat16 sw[GT][MK + MPAD];
-    __shared__ int s_src[GT], s_dst[GT];
+    __shared__ int s_src[MT], s_dst[MT];
     const int e = tile_expert[ti], p0 = tile_p0[ti], rows = tile_n[ti];
     const int n0 = blockIdx.x * GT;
-    if (threadIdx.x < GT) {
+    {
         const int r = threadIdx.x;
         int src = -1, dst = -1;
         if (r < rows) {
@@ -219,71 +223,87 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
     __syncthreads();
     const __nv_bfloat16 *we = w + (size_t)e * N * K;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    // the two 16-byte pieces of each operand this thread moves per 32 of k
-    const int vrow[2] = {(int)threadIdx.x / 4, (int)threadIdx.x / 4 + 32}, vk = (threadIdx.x & 3) * 8;
-    const __nv_bfloat16 *pa[2], *pw[2];
+    const bool live0 = 32 * warp < rows, live1 = 32 * warp + 16 < rows;          // this warp's two 16-place halves
+    // the 16-byte pieces this thread moves per 32 of k: four of the places' rows, two of the weights' rows
+    const int vr = threadIdx.x >> 2, vk = (threadIdx.x & 3) * 8;
+    const __nv_bfloat16 *pa[4], *pw[2];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int src = s_src[vr + 32 * i];
+        pa[i] = src >= 0 ? a + (size_t)src * K + vk : nullptr;
+    }
 #pragma unroll
     for (int i = 0; i < 2; i++) {
-        const int src = s_src[vrow[i]], gn = n0 + vrow[i];
-        pa[i] = src >= 0 ? a + (size_t)src * K + vk : nullptr;
+        const int gn = n0 + vr + 32 * i;
         pw[i] = gn < N ? we + (size_t)gn * K + vk : nullptr;
     }
-    uint4 ra[2], rw[2];
+    uint4 ra[4], rw[2];
     const uint4 zero = make_uint4(0, 0, 0, 0);
     auto fetch = [&](int k0) {
+        const bool in = k0 + vk < K;
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const bool in = k0 + vk < K;
-            ra[i] = (pa[i] && in) ? *(const uint4 *)(pa[i] + k0) : zero;
-            rw[i] = (pw[i] && in) ? *(const uint4 *)(pw[i] + k0) : zero;
-        }
+        for (int i = 0; i < 4; i++) ra[i] = (pa[i] && in) ? *(const uint4 *)(pa[i] + k0) : zero;
+#pragma unroll
+        for (int i = 0; i < 2; i++) rw[i] = (pw[i] && in) ? *(const uint4 *)(pw[i] + k0) : zero;
     };
-    float acc[8][4];
+    float acc[2][8][4];
 #pragma unroll
-    for (int i = 0; i < 8; i++)
+    for (int m = 0; m < 2; m++)
 #pragma unroll
-        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+        for (int i = 0; i < 8; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[m][i][j] = 0.f;
+    // ldmatrix row addresses: A 16x16 = (rows 0-7 | 8-15) x (k 0-7 | 8-15); B pairs of 8-feature tiles x (k 0-7 | 8-15)
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
+    const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
     fetch(0);
     for (int k0 = 0; k0 < K; k0 += MK) {
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-            *(uint4 *)&sa[vrow[i]][vk] = ra[i];
-            *(uint4 *)&sw[vrow[i]][vk] = rw[i];
-        }
+        for (int i = 0; i < 4; i++) *(uint4 *)&sa[vr + 32 * i][vk] = ra[i];
+#pragma unroll
+        for (int i = 0; i < 2; i++) *(uint4 *)&sw[vr + 32 * i][vk] = rw[i];
         __syncthreads();
         if (k0 + MK < K) fetch(k0 + MK);
+        if (live0) {
 #pragma unroll
-        for (int ks = 0; ks < MK; ks += 16) {
-            uint32_t af[4];
-            af[0] = *(const uint32_t *)&sa[16 * warp + g][ks + 2 * t];
-            af[1] = *(const uint32_t *)&sa[16 * warp + g + 8][ks + 2 * t];
-            af[2] = *(const uint32_t *)&sa[16 * warp + g][ks + 2 * t + 8];
-            af[3] = *(const uint32_t *)&sa[16 * warp + g + 8][ks + 2 * t + 8];
+            for (int ks = 0; ks < MK; ks += 16) {
+                uint32_t af[2][4];
+                ldmatrix_x4(af[0], &sa[32 * warp + a_row][ks + a_col]);
+                if (live1) ldmatrix_x4(af[1], &sa[32 * warp + 16 + a_row][ks + a_col]);
 #pragma unroll
-            for (int nt = 0; nt < 8; nt++) {
-                const uint32_t b0 = *(const uint32_t *)&sw[nt * 8 + g][ks + 2 * t];
-                const uint32_t b1 = *(const uint32_t *)&sw[nt * 8 + g][ks + 2 * t + 8];
-                mma_bf16(acc[nt], af, b0, b1);
+                for (int np = 0; np < 4; np++) {
+                    uint32_t bf[4];
+                    ldmatrix_x4(bf, &sw[np * 16 + b_row][ks + b_col]);
+                    mma_bf16(acc[0][2 * np], af[0], bf[0], bf[1]);
+                    mma_bf16(acc[0][2 * np + 1], af[0], bf[2], bf[3]);
+                    if (live1) {
+                        mma_bf16(acc[1][2 * np], af[1], bf[0], bf[1]);
+                        mma_bf16(acc[1][2 * np + 1], af[1], bf[2], bf[3]);
+                    }
+                }
             }
         }
         __syncthreads();
     }
 #pragma unroll
-    for (int half = 0; half < 2; half++) {
-        const int dst = s_dst[16 * warp + g + 8 * half];
-        if (dst < 0) continue;
+    for (int m = 0; m < 2; m++) {
 #pragma unroll
-        for (int nt = 0; nt < 8; nt++) {
+        for (int half = 0; half < 2; half++) {
+            const int dst = s_dst[32 * warp + 16 * m + g + 8 * half];
+            if (dst < 0) continue;
 #pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const int gn = n0 + nt * 8 + 2 * t + j;
-                if (gn >= N) continue;
-                float v = acc[nt][2 * half + j];
-                if (act == HFB_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
-                else if (act == HFB_ACT_RELU) v = fmaxf(v, 0.f);
-                else if (act == HFB_ACT_SILU) v = v / (1.0f + expf(-v));
-                else if (act == HFB_ACT_GELU_TANH) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
-                store_any(out, out_dt, (size_t)dst * N + gn, v);
+            for (int nt = 0; nt < 8; nt++) {
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const int gn = n0 + nt * 8 + 2 * t + j;
+                    if (gn >= N) continue;
+                    float v = acc[m][nt][2 * half + j];
+                    if (act == HFB_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
+                    else if (act == HFB_ACT_RELU) v = fmaxf(v, 0.f);
+                    else if (act == HFB_ACT_SILU) v = v / (1.0f + expf(-v));
+                    else if (act == HFB_ACT_GELU_TANH) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+                    store_any(out, out_dt, (size_t)dst * N + gn, v);
+                }
             }
         }
     }
@@ -315,23 +335,14 @@ static bool plain_products()
     return v != 0;
 }
 
-extern "C" int hfb_moe_route(const void *h, int h_dt, const void *w, const void *b, int w_dt, int T, int K, int E, int top,
-                             int32_t *ids, float *weights, hfb_stream s)
+extern "C" int hfb_moe_topk(const float *z, int T, int E, int top, int32_t *ids, float *weights, hfb_stream s)
 {
     if (T <= 0) return HFB_OK;
-    if (!valid_dt(h_dt) || !valid_dt(w_dt) || K <= 0 || E <= 0 || top <= 0 || top > E)
-        return fail(HFB_EINVAL, "moe_route: bad arguments (K=%d experts=%d top=%d)", K, E, top);
+    if (E <= 0 || top <= 0 || top > E) return fail(HFB_EINVAL, "moe_topk: bad arguments (experts=%d top=%d)", E, top);
     const size_t smem = (size_t)ROUTE_WARPS * (E + top) * sizeof(float);
-    if (smem > 48 * 1024) return fail(HFB_ENOTSUP, "moe_route: %d experts are more than the router kernel takes", E);
-    const dim3 grid((T + ROUTE_WARPS - 1) / ROUTE_WARPS), block(ROUTE_WARPS * 32);
-    cudaStream_t st = (cudaStream_t)s;
-#define LAUNCH(TH, TW) g_launch_err = launch_pdl(moe_route_kernel<TH, TW>, grid, block, smem, st, (const TH *)h, (const TW *)w, (const TW *)b, T, K, E, top, ids, weights)
-    if (h_dt == HFB_F32 && w_dt == HFB_F32) LAUNCH(float, float);
-    else if (h_dt == HFB_F32) LAUNCH(float, __nv_bfloat16);
-    else if (w_dt == HFB_F32) LAUNCH(__nv_bfloat16, float);
-    else LAUNCH(__nv_bfloat16, __nv_bfloat16);
-#undef LAUNCH
-    return check_pdl_launch(g_launch_err, "moe_route");
+    if (smem > 48 * 1024) return fail(HFB_ENOTSUP, "moe_topk: %d experts are more than the kernel takes", E);
+    g_launch_err = launch_pdl(moe_topk_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, (cudaStream_t)s, z, T, E, top, ids, weights);
+    return check_pdl_launch(g_launch_err, "moe_topk");
 }
 
 extern "C" int hfb_moe_max_tiles(int pairs, int E, int tile)
@@ -356,7 +367,7 @@ extern "C" int hfb_moe_gemm(const void *a, int a_dt, const void *w, int w_dt, vo
                             const int32_t *tile_n, const int32_t *n_tiles, int max_tiles, int tile, hfb_stream s)
 {
     if (max_tiles <= 0) return HFB_OK;
-    if (!valid_dt(a_dt) || !valid_dt(w_dt) || !valid_dt(out_dt) || N <= 0 || K <= 0 || tile != GT || act < 0 || act > HFB_ACT_NONE)
+    if (!valid_dt(a_dt) || !valid_dt(w_dt) || !valid_dt(out_dt) || N <= 0 || K <= 0 || tile != MT || act < 0 || act > HFB_ACT_NONE)
         return fail(HFB_EINVAL, "moe_gemm: bad arguments (N=%d K=%d tile=%d)", N, K, tile);
     if (max_tiles > 65535) return fail(HFB_ENOTSUP, "moe_gemm: %d tiles exceed the grid", max_tiles);
     const dim3 grid((N + GT - 1) / GT, max_tiles);
@@ -367,7 +378,7 @@ extern "C" int hfb_moe_gemm(const void *a, int a_dt, const void *w, int w_dt, vo
                                   order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles);
         return check_pdl_launch(g_launch_err, "moe_gemm_mma");
     }
-#define LAUNCH(TA, TW) g_launch_err = launch_pdl(moe_gemm_kernel<TA, TW>, grid, dim3(256), 0, st, (const TA *)a, (const TW *)w, out, out_dt, act, N, K, order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles)
+#define LAUNCH(TA, TW) g_launch_err = launch_pdl(moe_gemm_kernel<TA, TW>, dim3(grid.x, grid.y, MT / GT), dim3(256), 0, st, (const TA *)a, (const TW *)w, out, out_dt, act, N, K, order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles)
     if (a_dt == HFB_F32 && w_dt == HFB_F32) LAUNCH(float, float);
     else if (a_dt == HFB_F32) LAUNCH(float, __nv_bfloat16);
     else if (w_dt == HFB_F32) LAUNCH(__nv_bfloat16, float);

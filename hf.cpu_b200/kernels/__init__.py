@@ -208,7 +208,7 @@ def linear_rope_kv(a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out,
 
 
 ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "relu2": 3, "none": 4}       # relu2: the square of relu
-MOE_TILE = 64               # places of one expert per tile of the grouped product
+MOE_TILE = 128              # places of one expert per tile of the grouped product
 
 
 def _act(name: str) -> int:
@@ -284,14 +284,16 @@ def scale_(x: torch.Tensor, s: float) -> None:
     backend().scale_(x, float(s))
 
 
-def moe_route(h, w, b, top: int, ids, weights) -> None:
-    """Router: z = h @ w.T + b in float32; the ``top`` largest logits of a token choose its experts (``ids`` int32
-    [T, top], largest first, the lower index among equals), ``weights`` = softmax over the chosen logits only."""
+def moe_route(h, w, b, top: int, ids, weights, logits) -> None:
+    """Router: ``logits`` = h @ w.T + b accumulated in float32 (a product like any other: exact products of the stored
+    values, float32 sums); the ``top`` largest logits of a token choose its experts (``ids`` int32 [T, top], largest
+    first, the lower index among equals), ``weights`` = softmax over the chosen logits only."""
     T, E = h.shape[0], w.shape[0]
     _need(h.shape[1] == w.shape[1] and (b is None or b.shape == (E,)) and 1 <= top <= E, "moe_route: shape mismatch")
     _need(ids.shape == (T, top) and ids.dtype == torch.int32 and weights.shape == (T, top) and weights.dtype == torch.float32,
           "moe_route: ids int32 [T, top], weights float32 [T, top]")
-    backend().moe_route(h, w, b, int(top), ids, weights)
+    _need(logits.shape == (T, E) and logits.dtype == torch.float32, "moe_route: logits float32 [T, experts]")
+    backend().moe_route(h, w, b, int(top), ids, weights, logits)
 
 
 def moe_max_tiles(pairs: int, experts: int) -> int:

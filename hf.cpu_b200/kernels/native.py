@@ -391,11 +391,12 @@ class NativeBackend:
         self._on_gpu(x)
         self._check(self.lib.hfb_scale(_p(x), c_int64(x.numel()), c_float(s), self._stream()), "scale")
 
-    def moe_route(self, h, w, b, top, ids, weights):
-        self._on_gpu(h, w, b, ids, weights)
-        T, K = h.shape
-        self._check(self.lib.hfb_moe_route(_p(h), c_int(_dt(h)), _p(w), _p(b), c_int(_dt(w)), c_int(T), c_int(K),
-                                           c_int(w.shape[0]), c_int(top), _p(ids), _p(weights), self._stream()), "moe_route")
+    def moe_route(self, h, w, b, top, ids, weights, logits):
+        self._on_gpu(h, w, b, ids, weights, logits)
+        self.linear(h, w, b, logits, False)
+        T, E = logits.shape
+        self._check(self.lib.hfb_moe_topk(_p(logits), c_int(T), c_int(E), c_int(top), _p(ids), _p(weights), self._stream()),
+                    "moe_topk")
 
     def moe_group(self, ids, experts, order, tile_expert, tile_p0, tile_n, n_tiles):
         self._on_gpu(ids, order, tile_expert, tile_p0, tile_n, n_tiles)

@@ -76,8 +76,9 @@ class MoeFfn(FeedForward):
         i32 = torch.int32
         ids = ctx.buf("moe_ids", (T, self.top), i32)
         wts = ctx.buf("moe_weights", (T, self.top), torch.float32)
+        z = ctx.buf("moe_logits", (T, self.n), torch.float32)
         with kernels.phase("glue"):
-            kernels.moe_route(xn, self.w_router, self.b_router, self.top, ids, wts)
+            kernels.moe_route(xn, self.w_router, self.b_router, self.top, ids, wts, z)
             mt = kernels.moe_max_tiles(P, self.n)
             order = ctx.buf("moe_order", (P,), i32)
             tiles = [ctx.buf(f"moe_tile{k}", (mt,), i32) for k in range(3)]

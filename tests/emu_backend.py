@@ -156,10 +156,11 @@ class EmuBackend:
     def scale_(self, x, s):
         x.mul_(s)
 
-    def moe_route(self, h, w, b, top, ids, weights):
+    def moe_route(self, h, w, b, top, ids, weights, logits):
         z = h.float() @ w.float().T
         if b is not None:
             z = z + b.float()
+        logits.copy_(z)
         zc, idx = torch.sort(z, dim=-1, descending=True, stable=True)
         ids.copy_(idx[:, :top].int())
         weights.copy_(torch.softmax(zc[:, :top], -1))

@@ -121,7 +121,7 @@ def test_router_top_k_and_softmax_over_the_chosen(dtype, geom):
     h, w, b = dev(r.standard_normal((T, Kd)), dt), dev(r.standard_normal((E, Kd)), dt), dev(2 * r.standard_normal(E), dt)
     ids = torch.empty(T, top, dtype=torch.int32, device=DEV)
     wts = torch.empty(T, top, dtype=torch.float32, device=DEV)
-    K().moe_route(h, w, b, top, ids, wts)
+    K().moe_route(h, w, b, top, ids, wts, torch.empty(T, E, dtype=torch.float32, device=DEV))
     W = {"m.router": w.double().cpu().numpy(), "m.router.b": b.double().cpu().numpy()}
     want_ids, want_w = plain.route(h.double().cpu().numpy(), W, "m", top)
     assert np.array_equal(ids.cpu().numpy(), want_ids)
@@ -344,7 +344,7 @@ def test_planted_far_key_at_page_borders(folders, tmp_path, name, dtype):
         without[far] = 8
         miss = plain.forward(C, W, without)[-1]
         matters = np.abs(want - miss).max() / np.abs(want).max()
-        assert matters > (0.05 if dtype == "bfloat16" else 10 * tol), f"the planted key does not matter enough ({matters:.3g})"
+        assert matters > (0.03 if dtype == "bfloat16" else 10 * tol), f"the planted key does not matter enough ({matters:.3g})"
         if dtype == "bfloat16":
             tol = 0.3 * matters                            # far closer to the right answer than to the one without the key
         for tail in (5, 1):
