@@ -1,4 +1,4 @@
-"""A B200-native inference engine for the Qwen2 dense decoder, shaped after the CPU engine hf.cpu.
+"""A B200-native inference engine for the Qwen2 dense decoder (and the Manapel decoder), shaped after the CPU engine hf.cpu.
 
 Sub-packages: ``config`` (typed configuration, registry), ``weights`` (safetensors by name, random
 weights), ``parts`` (norm, position encoding, mixer, feed-forward, block), ``models`` (a model put

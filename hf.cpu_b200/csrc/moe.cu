@@ -196,6 +196,18 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *p)
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
+constexpr int MSTAGES = 3;
+
+__device__ __forceinline__ void cp_async_16(void *smem, const void *gmem, bool valid)
+{
+    // 16 bytes global -> shared without passing registers; src-size 0 fills the 16 bytes with zeros instead
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem);
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__restrict__ w, void *out, int out_dt, int act,
                     int N, int K, const int32_t *order, int src_div, int scatter, const int32_t *tile_expert,
@@ -204,8 +216,8 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
     pdl_sync();
     const int ti = blockIdx.y;
     if (ti >= *n_tiles) return;
-    __shared__ __align__(16) __nv_bfloat16 sa[MT][MK + MPAD];
-    __shared__ __align__(16) __nv_bfloat16 sw[GT][MK + MPAD];
+    __shared__ __align__(16) __nv_bfloat16 sa[MSTAGES][MT][MK + MPAD];
+    __shared__ __align__(16) __nv_bfloat16 sw[MSTAGES][GT][MK + MPAD];
     __shared__ int s_src[MT], s_dst[MT];
     const int e = tile_expert[ti], p0 = tile_p0[ti], rows = tile_n[ti];
     const int n0 = blockIdx.x * GT;
@@ -237,14 +249,13 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
         const int gn = n0 + vr + 32 * i;
         pw[i] = gn < N ? we + (size_t)gn * K + vk : nullptr;
     }
-    uint4 ra[4], rw[2];
-    const uint4 zero = make_uint4(0, 0, 0, 0);
-    auto fetch = [&](int k0) {
+    // a piece of k on its way into stage `st` (rows that do not exist and k beyond K arrive as zeros)
+    auto fetch = [&](int k0, int st) {
         const bool in = k0 + vk < K;
 #pragma unroll
-        for (int i = 0; i < 4; i++) ra[i] = (pa[i] && in) ? *(const uint4 *)(pa[i] + k0) : zero;
+        for (int i = 0; i < 4; i++) cp_async_16(&sa[st][vr + 32 * i][vk], pa[i] && in ? pa[i] + k0 : a, pa[i] && in);
 #pragma unroll
-        for (int i = 0; i < 2; i++) rw[i] = (pw[i] && in) ? *(const uint4 *)(pw[i] + k0) : zero;
+        for (int i = 0; i < 2; i++) cp_async_16(&sw[st][vr + 32 * i][vk], pw[i] && in ? pw[i] + k0 : w, pw[i] && in);
     };
     float acc[2][8][4];
 #pragma unroll
@@ -256,24 +267,27 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
     // ldmatrix row addresses: A 16x16 = (rows 0-7 | 8-15) x (k 0-7 | 8-15); B pairs of 8-feature tiles x (k 0-7 | 8-15)
     const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
     const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
-    fetch(0);
-    for (int k0 = 0; k0 < K; k0 += MK) {
-#pragma unroll
-        for (int i = 0; i < 4; i++) *(uint4 *)&sa[vr + 32 * i][vk] = ra[i];
-#pragma unroll
-        for (int i = 0; i < 2; i++) *(uint4 *)&sw[vr + 32 * i][vk] = rw[i];
-        __syncthreads();
-        if (k0 + MK < K) fetch(k0 + MK);
+    const int chunks = (K + MK - 1) / MK;
+    fetch(0, 0);
+    cp_async_commit();
+    if (chunks > 1) fetch(MK, 1);
+    cp_async_commit();
+    for (int c = 0; c < chunks; c++) {
+        const int st = c % MSTAGES;
+        cp_async_wait<1>();                      // piece c has landed (one newer group may still be in flight)
+        __syncthreads();                         // ... for every thread, and piece c - 1 has been multiplied by all
+        if (c + 2 < chunks) fetch((c + 2) * MK, (c + 2) % MSTAGES);
+        cp_async_commit();
         if (live0) {
 #pragma unroll
             for (int ks = 0; ks < MK; ks += 16) {
                 uint32_t af[2][4];
-                ldmatrix_x4(af[0], &sa[32 * warp + a_row][ks + a_col]);
-                if (live1) ldmatrix_x4(af[1], &sa[32 * warp + 16 + a_row][ks + a_col]);
+                ldmatrix_x4(af[0], &sa[st][32 * warp + a_row][ks + a_col]);
+                if (live1) ldmatrix_x4(af[1], &sa[st][32 * warp + 16 + a_row][ks + a_col]);
 #pragma unroll
                 for (int np = 0; np < 4; np++) {
                     uint32_t bf[4];
-                    ldmatrix_x4(bf, &sw[np * 16 + b_row][ks + b_col]);
+                    ldmatrix_x4(bf, &sw[st][np * 16 + b_row][ks + b_col]);
                     mma_bf16(acc[0][2 * np], af[0], bf[0], bf[1]);
                     mma_bf16(acc[0][2 * np + 1], af[0], bf[2], bf[3]);
                     if (live1) {
@@ -283,8 +297,8 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
                 }
             }
         }
-        __syncthreads();
     }
+    cp_async_wait<0>();
 #pragma unroll
     for (int m = 0; m < 2; m++) {
 #pragma unroll

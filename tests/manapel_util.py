@@ -42,8 +42,9 @@ WIDE = {"architecture": "Manapel", "vocab": 1032, "width": 256, "logit_scale": 0
     layer(att(4, 1, 128, 128, 64, 50000.0, 0.2), moe(3, 2, 128)),
     layer(att(4, 1, 128, 128, 64, 50000.0, 0.2, kv_from=2), moe(16, 1, 64, shared=64)),
 ]}
-# One key/value head per query head, no rotation in one layer, a value head narrower than the key head.
-THIN = {"architecture": "Manapel", "vocab": 97, "width": 40, "logit_scale": 1.0, "norm": {"eps": 1e-5}, "layers": [
+# One key/value head per query head, no rotation in one layer, a value head narrower than the key head, a width that is
+# no multiple of 8 (no tensor-core product takes it).
+THIN = {"architecture": "Manapel", "vocab": 97, "width": 44, "logit_scale": 1.0, "norm": {"eps": 1e-5}, "layers": [
     layer(att(2, 2, 32, 8, None, 0.0, 0.4), {"kind": "dense", "ff": 24}),
     layer(att(2, 1, 20, 12, 4, 77.0, 0.9), moe(2, 2, 16, shared=8)),
 ]}
