@@ -31,10 +31,11 @@ __global__ void dyt_kernel(const TX *x, const int32_t *rows, DytParams p, void *
     }
 }
 
-// residual[m, c] += dyt(y[m, c]); with `next`: out[m, c] = dyt_next(residual[m, c])
+// residual[m, c] += dyt(y[m, c]); with `next`: out[m, c] = dyt_next(residual[m, c]).  y may come as `splits` partial
+// sums [splits, M, E] of a product (summed in split order) with the product's bias still to add.
 template <typename TY>
-__global__ void dyt_residual_kernel(const TY *y, DytParams p, float *residual, int has_next, DytParams next, void *out,
-                                    int out_dt, int M, int E)
+__global__ void dyt_residual_kernel(const TY *y, int splits, const void *bias, int bias_dt, DytParams p, float *residual,
+                                    int has_next, DytParams next, void *out, int out_dt, int M, int E)
 {
     pdl_entry();
     pdl_sync_small();
@@ -43,7 +44,10 @@ __global__ void dyt_residual_kernel(const TY *y, DytParams p, float *residual, i
     const size_t total = (size_t)M * E;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int c = (int)(i % E);
-        const float r = residual[i] + dyt_one(p, alpha, to_f32(y[i]), c);
+        float v = to_f32(y[i]);
+        for (int s = 1; s < splits; s++) v += to_f32(y[(size_t)s * total + i]);
+        if (bias) v += load_any(bias, bias_dt, c);
+        const float r = residual[i] + dyt_one(p, alpha, v, c);
         residual[i] = r;
         if (has_next) store_any(out, out_dt, i, dyt_one(next, alpha2, r, c));
     }
@@ -115,19 +119,19 @@ extern "C" int hfb_dyt(const void *x, int x_dt, const int32_t *rows, const void 
     return check_pdl_launch(g_launch_err, "dyt");
 }
 
-extern "C" int hfb_dyt_residual(const void *y, int y_dt, const void *alpha, const void *w, const void *b, int p_dt,
+extern "C" int hfb_dyt_residual(const void *y, int y_dt, int splits, const void *bias, int bias_dt, const void *alpha, const void *w, const void *b, int p_dt,
                                 float *residual, const void *alpha2, const void *w2, const void *b2, int p2_dt,
                                 void *out, int out_dt, int M, int E, hfb_stream s)
 {
     if (M <= 0) return HFB_OK;
     const int has_next = out != nullptr;
-    if (!valid_dt(y_dt) || !valid_dt(p_dt) || E <= 0 || !alpha || !w || !b || !residual ||
+    if (!valid_dt(y_dt) || !valid_dt(p_dt) || E <= 0 || !alpha || !w || !b || !residual || splits < 1 || (bias && !valid_dt(bias_dt)) ||
         (has_next && (!alpha2 || !w2 || !b2 || !valid_dt(p2_dt) || !valid_dt(out_dt))))
         return fail(HFB_EINVAL, "dyt_residual: bad arguments");
     DytParams p{alpha, w, b, p_dt}, n{alpha2, w2, b2, p2_dt};
     const unsigned blocks = blocks_for((size_t)M * E);
-    if (y_dt == HFB_F32) g_launch_err = launch_pdl(dyt_residual_kernel<float>, dim3(blocks), dim3(256), 0, (cudaStream_t)s, (const float *)y, p, residual, has_next, n, out, out_dt, M, E);
-    else g_launch_err = launch_pdl(dyt_residual_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, (cudaStream_t)s, (const __nv_bfloat16 *)y, p, residual, has_next, n, out, out_dt, M, E);
+    if (y_dt == HFB_F32) g_launch_err = launch_pdl(dyt_residual_kernel<float>, dim3(blocks), dim3(256), 0, (cudaStream_t)s, (const float *)y, splits, bias, bias_dt, p, residual, has_next, n, out, out_dt, M, E);
+    else g_launch_err = launch_pdl(dyt_residual_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, (cudaStream_t)s, (const __nv_bfloat16 *)y, splits, bias, bias_dt, p, residual, has_next, n, out, out_dt, M, E);
     return check_pdl_launch(g_launch_err, "dyt_residual");
 }
 

@@ -160,8 +160,9 @@ int hfb_scale(float *x, int64_t total, float scale, hfb_stream s);
 int hfb_dyt(const void *x, int x_dt, const int32_t *rows, const void *alpha, const void *w, const void *b,
             int p_dt, void *out, int out_dt, int M, int E, hfb_stream s);
 
-/* residual += dyt(y); with out != NULL also out = dyt2(residual) (the next sublayer's input). */
-int hfb_dyt_residual(const void *y, int y_dt, const void *alpha, const void *w, const void *b, int p_dt,
+/* residual += dyt(y); with out != NULL also out = dyt2(residual) (the next sublayer's input).  y [splits, M, E]: partial
+ * sums of a product, summed in order, plus its bias (null: none); a finished y has splits = 1. */
+int hfb_dyt_residual(const void *y, int y_dt, int splits, const void *bias, int bias_dt, const void *alpha, const void *w, const void *b, int p_dt,
                      float *residual, const void *alpha2, const void *w2, const void *b2, int p2_dt,
                      void *out, int out_dt, int M, int E, hfb_stream s);
 

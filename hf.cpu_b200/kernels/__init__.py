@@ -244,6 +244,20 @@ def dyt_residual(y: torch.Tensor, post, residual: torch.Tensor, nxt=None, out: O
     backend().dyt_residual(y, post, residual, nxt, out)
 
 
+def linear_dyt_residual(a, w, bias, y_buf, post, residual, nxt=None, out=None) -> None:
+    """residual += dyt_post(a @ w.T + bias), and with ``nxt`` / ``out`` the next norm of the new residual, as
+    :func:`dyt_residual`; ``y_buf`` [M, N] float32 is scratch for the form that finishes the product first."""
+    _need(a.shape[1] == w.shape[1] and residual.shape == (a.shape[0], w.shape[0]) and residual.dtype == torch.float32,
+          "linear_dyt_residual: shape mismatch")
+    _need(y_buf.shape == residual.shape and y_buf.dtype == torch.float32, "linear_dyt_residual: scratch must be float32 [M, N]")
+    _dyt_ok(post, w.shape[0], "linear_dyt_residual")
+    _need((nxt is None) == (out is None), "linear_dyt_residual: the next norm and its output come together")
+    if nxt is not None:
+        _dyt_ok(nxt, w.shape[0], "linear_dyt_residual")
+        _need(out.shape == residual.shape, "linear_dyt_residual: output shape mismatch")
+    backend().linear_dyt_residual(a, w, bias, y_buf, post, residual, nxt, out)
+
+
 def linear_rope_norm_kv(a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d, dv,
                         norm_eps) -> None:
     """The q|k|v product and its tail for attention with unit-rms queries and keys: row = [H heads of d | G key heads

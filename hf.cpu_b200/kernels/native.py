@@ -338,12 +338,23 @@ class NativeBackend:
         self._check(self.lib.hfb_dyt(_p(x), c_int(_dt(x)), _p(rows), _p(alpha), _p(w), _p(b), c_int(_dt(w)), _p(out),
                                      c_int(_dt(out)), c_int(M), c_int(E), self._stream()), "dyt")
 
-    def dyt_residual(self, y, post, residual, nxt, out):
-        self._on_gpu(y, *post, residual, out, *(nxt or ()))
+    def linear_dyt_residual(self, a, w, bias, y_buf, post, residual, nxt, out):
+        """residual += dyt(a @ w.T + bias): the product's split-K partial sums are summed by the norm's own pass
+        where the product is split, else it stores float32 to ``y_buf`` first."""
+        self._on_gpu(a, w, bias, y_buf)
+        part = self._partials(a, w) if self._tc_ok(a, w) else None
+        if part is None:
+            self.linear(a, w, bias, y_buf, False)
+            self.dyt_residual(y_buf, post, residual, nxt, out)
+        else:
+            self.dyt_residual(part[0], post, residual, nxt, out, splits=part[1], bias=bias, as_f32=True)
+
+    def dyt_residual(self, y, post, residual, nxt, out, splits=1, bias=None, as_f32=False):
+        self._on_gpu(*post, residual, out, *(nxt or ()))
         M, E = residual.shape
         n = nxt or (None, None, None)
         self._check(self.lib.hfb_dyt_residual(
-            _p(y), c_int(_dt(y)), _p(post[0]), _p(post[1]), _p(post[2]), c_int(_dt(post[1])), _p(residual), _p(n[0]), _p(n[1]),
+            _p(y), c_int(F32 if as_f32 else _dt(y)), c_int(splits), _p(bias), c_int(_dt(bias) if bias is not None else 0), _p(post[0]), _p(post[1]), _p(post[2]), c_int(_dt(post[1])), _p(residual), _p(n[0]), _p(n[1]),
             _p(n[2]), c_int(_dt(n[1]) if nxt else 0), _p(out), c_int(_dt(out) if out is not None else 0), c_int(M), c_int(E),
             self._stream()), "dyt_residual")
 

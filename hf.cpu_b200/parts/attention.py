@@ -152,6 +152,12 @@ class PagedAttention(Mixer):
         with kernels.phase("wo"):
             kernels.linear(att, self.w_o, self.b_o, residual, accumulate=accumulate)
 
+    def forward_into_norm(self, ctx, xn, cache, state, write_cache, y_buf, residual, post, next_norm, out):
+        """residual += post(mixer output), the output product handed to the norm (see ``DynamicTanh.add_product_into``)."""
+        att = self._attend(ctx, xn, cache, write_cache)
+        with kernels.phase("wo"):
+            return post.add_product_into(att, self.w_o, self.b_o, y_buf, residual, next_norm, out)
+
     def forward_then_norm(self, ctx, xn, residual, cache, state, write_cache, norm, out):
         args = norm.fused_args()
         if args is None:

@@ -55,16 +55,23 @@ class SandwichResidual(Block):
         else:
             xn = xn_ready
         y = ctx.buf("block_y", x.shape, torch.float32)
-        mixer.forward(ctx, xn, y, cache, state, write_cache, accumulate=False)
+
+        def sublayer(part, post, nn, out, *args):
+            """x += post(part(...)); returns whether ``out = nn(x)`` came out of the same pass.  A part whose output is a
+            product hands that product to the norm (``forward_into_norm``), which may sum its partial sums itself."""
+            into = getattr(part, "forward_into_norm", None) if hasattr(post, "add_product_into") else None
+            if into is not None:
+                return into(ctx, *args, y, x, post, nn, out)
+            part.forward(ctx, *args, y, accumulate=False) if part is ffn else part.forward(ctx, *args[:1], y, *args[1:], accumulate=False)
+            return post.add_into(y, x, nn, out)
         if ffn is None:
             nxt = ctx.buf("block_xn", x.shape, ctx.run_dtype) if next_norm is not None else None
-            return nxt if post1.add_into(y, x, next_norm, nxt) else None
+            return nxt if sublayer(mixer, post1, next_norm, nxt, xn, cache, state, write_cache) else None
         xn2 = ctx.buf("block_xn2", x.shape, ctx.run_dtype)
-        if not post1.add_into(y, x, norm2, xn2):
+        if not sublayer(mixer, post1, norm2, xn2, xn, cache, state, write_cache):
             norm2.forward(x, xn2)
-        ffn.forward(ctx, xn2, y, accumulate=False)
         nxt = ctx.buf("block_xn", x.shape, ctx.run_dtype) if next_norm is not None else None
-        return nxt if post2.add_into(y, x, next_norm, nxt) else None
+        return nxt if sublayer(ffn, post2, next_norm, nxt, xn2) else None
 
 
 register_part("block", "prenorm_residual", PreNormResidual)

@@ -55,6 +55,12 @@ class SwiGlu(FeedForward):
         with kernels.phase("down"):
             kernels.linear(h, self.w_down, None, residual, accumulate=accumulate)
 
+    def forward_into_norm(self, ctx, xn, y_buf, residual, post, next_norm, out):
+        """residual += post(feed-forward output), the down product handed to the norm."""
+        h = self._hidden(ctx, xn)
+        with kernels.phase("down"):
+            return post.add_product_into(h, self.w_down, None, y_buf, residual, next_norm, out)
+
     def forward_then_norm(self, ctx, xn, residual, norm, out):
         args = norm.fused_args()
         if args is None:

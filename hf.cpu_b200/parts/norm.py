@@ -68,6 +68,14 @@ class DynamicTanh(Norm):
             kernels.dyt_residual(y, self.params, residual, next_norm.params if fused else None, out if fused else None)
         return fused
 
+    def add_product_into(self, a, w, bias, y_buf, residual, next_norm=None, out=None):
+        """The same for a sublayer whose output is a product, ``a @ w.T + bias``: where the product is split over its
+        inner dimension, the partial sums are summed by this norm's own pass."""
+        fused = out is not None and isinstance(next_norm, DynamicTanh)
+        kernels.linear_dyt_residual(a, w, bias, y_buf, self.params, residual, next_norm.params if fused else None,
+                                    out if fused else None)
+        return fused
+
 
 register_part("norm", "rmsnorm", RmsNorm)
 register_part("norm", "dynamic_tanh", DynamicTanh)

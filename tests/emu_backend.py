@@ -109,6 +109,10 @@ class EmuBackend:
         if nxt is not None:
             out.copy_(self._dyt(residual, nxt).to(out.dtype))
 
+    def linear_dyt_residual(self, a, w, bias, y_buf, post, residual, nxt, out):
+        self.linear(a, w, bias, y_buf, False)
+        self.dyt_residual(y_buf, post, residual, nxt, out)
+
     def linear_rope_norm_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d, dv,
                             norm_eps):
         self.linear(a, w, bias, qkv_buf, False)
