@@ -175,9 +175,9 @@ moe_gemm_kernel(const TA *__restrict__ a, const TW *__restrict__ w, void *out, i
 }
 
 // The same grouped product for bfloat16 operands on the tensor cores (mma.sync m16n8k16, float32 accumulators): a tile
-// of 128 places x 64 features, four warps of 32 places each; operands go through registers into padded shared memory,
-// 32 of k at a time, the next piece on its way while the current one is multiplied; fragments come out of shared
-// memory with ldmatrix.x4.  A warp whose places lie beyond the tile's count multiplies nothing (a step of single
+// of 128 places x 128 features, eight warps of 32 places x 64 features each; operands come into padded shared memory
+// by cp.async, 32 of k at a time in three stages, so that two pieces are on their way while one is multiplied;
+// fragments come out of shared memory with ldmatrix.x4.  A warp whose places lie beyond the tile's count multiplies nothing (a step of single
 // tokens has a handful of places per expert).  K is a multiple of 8 and the operands are 16-byte aligned (every
 // 16-byte piece of a row lies wholly inside or outside K).
 constexpr int MT = 128, MK = 32, MPAD = 8;
@@ -208,7 +208,10 @@ __device__ __forceinline__ void cp_async_16(void *smem, const void *gmem, bool v
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-__global__ void __launch_bounds__(128)
+constexpr int MN = 128;                                       // features per tile of the tensor-core form
+constexpr size_t MMA_SMEM = (size_t)MSTAGES * (MT + MN) * (MK + MPAD) * sizeof(__nv_bfloat16) + 2 * MT * sizeof(int);
+
+__global__ void __launch_bounds__(256)
 moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__restrict__ w, void *out, int out_dt, int act,
                     int N, int K, const int32_t *order, int src_div, int scatter, const int32_t *tile_expert,
                     const int32_t *tile_p0, const int32_t *tile_n, const int32_t *n_tiles)
@@ -216,12 +219,15 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
     pdl_sync();
     const int ti = blockIdx.y;
     if (ti >= *n_tiles) return;
-    __shared__ __align__(16) __nv_bfloat16 sa[MSTAGES][MT][MK + MPAD];
-    __shared__ __align__(16) __nv_bfloat16 sw[MSTAGES][GT][MK + MPAD];
-    __shared__ int s_src[MT], s_dst[MT];
+    extern __shared__ __align__(16) uint8_t mma_smem[];
+    typedef __nv_bfloat16 (*Stage)[MK + MPAD];
+    __nv_bfloat16 *sa_base = (__nv_bfloat16 *)mma_smem, *sw_base = sa_base + (size_t)MSTAGES * MT * (MK + MPAD);
+    int *s_src = (int *)(sw_base + (size_t)MSTAGES * MN * (MK + MPAD)), *s_dst = s_src + MT;
+    auto sa = [&](int st) { return (Stage)(sa_base + (size_t)st * MT * (MK + MPAD)); };
+    auto sw = [&](int st) { return (Stage)(sw_base + (size_t)st * MN * (MK + MPAD)); };
     const int e = tile_expert[ti], p0 = tile_p0[ti], rows = tile_n[ti];
-    const int n0 = blockIdx.x * GT;
-    {
+    const int n0 = blockIdx.x * MN;
+    if (threadIdx.x < MT) {
         const int r = threadIdx.x;
         int src = -1, dst = -1;
         if (r < rows) {
@@ -235,27 +241,25 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
     __syncthreads();
     const __nv_bfloat16 *we = w + (size_t)e * N * K;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const bool live0 = 32 * warp < rows, live1 = 32 * warp + 16 < rows;          // this warp's two 16-place halves
-    // the 16-byte pieces this thread moves per 32 of k: four of the places' rows, two of the weights' rows
+    const int wm = warp & 3, wn = warp >> 2;                // this warp: places 32 wm .. + 32, features 64 wn .. + 64
+    const bool live0 = 32 * wm < rows, live1 = 32 * wm + 16 < rows;
+    // the 16-byte pieces this thread moves per 32 of k: two of the places' rows, two of the weights' rows
     const int vr = threadIdx.x >> 2, vk = (threadIdx.x & 3) * 8;
-    const __nv_bfloat16 *pa[4], *pw[2];
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const int src = s_src[vr + 32 * i];
-        pa[i] = src >= 0 ? a + (size_t)src * K + vk : nullptr;
-    }
+    const __nv_bfloat16 *pa[2], *pw[2];
 #pragma unroll
     for (int i = 0; i < 2; i++) {
-        const int gn = n0 + vr + 32 * i;
+        const int src = s_src[vr + 64 * i], gn = n0 + vr + 64 * i;
+        pa[i] = src >= 0 ? a + (size_t)src * K + vk : nullptr;
         pw[i] = gn < N ? we + (size_t)gn * K + vk : nullptr;
     }
     // a piece of k on its way into stage `st` (rows that do not exist and k beyond K arrive as zeros)
     auto fetch = [&](int k0, int st) {
         const bool in = k0 + vk < K;
 #pragma unroll
-        for (int i = 0; i < 4; i++) cp_async_16(&sa[st][vr + 32 * i][vk], pa[i] && in ? pa[i] + k0 : a, pa[i] && in);
-#pragma unroll
-        for (int i = 0; i < 2; i++) cp_async_16(&sw[st][vr + 32 * i][vk], pw[i] && in ? pw[i] + k0 : w, pw[i] && in);
+        for (int i = 0; i < 2; i++) {
+            cp_async_16(&sa(st)[vr + 64 * i][vk], pa[i] && in ? pa[i] + k0 : a, pa[i] && in);
+            cp_async_16(&sw(st)[vr + 64 * i][vk], pw[i] && in ? pw[i] + k0 : w, pw[i] && in);
+        }
     };
     float acc[2][8][4];
 #pragma unroll
@@ -282,12 +286,12 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
 #pragma unroll
             for (int ks = 0; ks < MK; ks += 16) {
                 uint32_t af[2][4];
-                ldmatrix_x4(af[0], &sa[st][32 * warp + a_row][ks + a_col]);
-                if (live1) ldmatrix_x4(af[1], &sa[st][32 * warp + 16 + a_row][ks + a_col]);
+                ldmatrix_x4(af[0], &sa(st)[32 * wm + a_row][ks + a_col]);
+                if (live1) ldmatrix_x4(af[1], &sa(st)[32 * wm + 16 + a_row][ks + a_col]);
 #pragma unroll
                 for (int np = 0; np < 4; np++) {
                     uint32_t bf[4];
-                    ldmatrix_x4(bf, &sw[st][np * 16 + b_row][ks + b_col]);
+                    ldmatrix_x4(bf, &sw(st)[64 * wn + np * 16 + b_row][ks + b_col]);
                     mma_bf16(acc[0][2 * np], af[0], bf[0], bf[1]);
                     mma_bf16(acc[0][2 * np + 1], af[0], bf[2], bf[3]);
                     if (live1) {
@@ -303,13 +307,13 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
     for (int m = 0; m < 2; m++) {
 #pragma unroll
         for (int half = 0; half < 2; half++) {
-            const int dst = s_dst[32 * warp + 16 * m + g + 8 * half];
+            const int dst = s_dst[32 * wm + 16 * m + g + 8 * half];
             if (dst < 0) continue;
 #pragma unroll
             for (int nt = 0; nt < 8; nt++) {
 #pragma unroll
                 for (int j = 0; j < 2; j++) {
-                    const int gn = n0 + nt * 8 + 2 * t + j;
+                    const int gn = n0 + 64 * wn + nt * 8 + 2 * t + j;
                     if (gn >= N) continue;
                     float v = acc[m][nt][2 * half + j];
                     if (act == HFB_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
@@ -388,7 +392,14 @@ extern "C" int hfb_moe_gemm(const void *a, int a_dt, const void *w, int w_dt, vo
     cudaStream_t st = (cudaStream_t)s;
     if (a_dt == HFB_BF16 && w_dt == HFB_BF16 && (K & 7) == 0 && ((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0 &&
         !plain_products()) {
-        g_launch_err = launch_pdl(moe_gemm_mma_kernel, grid, dim3(128), 0, st, (const __nv_bfloat16 *)a, (const __nv_bfloat16 *)w, out, out_dt, act, N, K,
+        static bool opted[64] = {};              // more than 48 KB of shared memory: asked for once per device
+        const int dev = current_device();
+        if (!opted[dev]) {
+            if (cudaFuncSetAttribute(moe_gemm_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM) != cudaSuccess)
+                return fail(HFB_ECUDA, "moe_gemm: the kernel's shared memory could not be set");
+            opted[dev] = true;
+        }
+        g_launch_err = launch_pdl(moe_gemm_mma_kernel, dim3((N + MN - 1) / MN, max_tiles), dim3(256), MMA_SMEM, st, (const __nv_bfloat16 *)a, (const __nv_bfloat16 *)w, out, out_dt, act, N, K,
                                   order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles);
         return check_pdl_launch(g_launch_err, "moe_gemm_mma");
     }
