@@ -31,10 +31,12 @@ __global__ void dyt_kernel(const TX *x, const int32_t *rows, DytParams p, void *
     }
 }
 
-// residual[m, c] += dyt(y[m, c]); with `next`: out[m, c] = dyt_next(residual[m, c]).  y may come as `splits` partial
-// sums [splits, M, E] of a product (summed in split order) with the product's bias still to add.
+// residual[m, c] += dyt(y[m, c]); with `next`: out[m, c] = dyt_next(residual[m, c]).  y may come in pieces that this
+// pass sums, in this order: `splits` partial sums [splits, M, E] of a product (none: splits = 0), the product's bias, and
+// the weighted sum of `top` rows per token, sum_j mix_w[m, j] * mix_y[m * top + j, c] (a routed feed-forward's experts).
 template <typename TY>
-__global__ void dyt_residual_kernel(const TY *y, int splits, const void *bias, int bias_dt, DytParams p, float *residual,
+__global__ void dyt_residual_kernel(const TY *y, int splits, const void *bias, int bias_dt, const float *mix_y,
+                                    const float *mix_w, int top, DytParams p, float *residual,
                                     int has_next, DytParams next, void *out, int out_dt, int M, int E)
 {
     pdl_entry();
@@ -44,9 +46,15 @@ __global__ void dyt_residual_kernel(const TY *y, int splits, const void *bias, i
     const size_t total = (size_t)M * E;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int c = (int)(i % E);
-        float v = to_f32(y[i]);
-        for (int s = 1; s < splits; s++) v += to_f32(y[(size_t)s * total + i]);
+        float v = 0.f;
+        for (int s = 0; s < splits; s++) v += to_f32(y[(size_t)s * total + i]);
         if (bias) v += load_any(bias, bias_dt, c);
+        if (mix_y) {
+            const size_t m = i / E;
+            float acc = 0.f;
+            for (int j = 0; j < top; j++) acc = fmaf(mix_w[m * top + j], mix_y[(m * top + j) * E + c], acc);
+            v += acc;
+        }
         const float r = residual[i] + dyt_one(p, alpha, v, c);
         residual[i] = r;
         if (has_next) store_any(out, out_dt, i, dyt_one(next, alpha2, r, c));
@@ -119,19 +127,21 @@ extern "C" int hfb_dyt(const void *x, int x_dt, const int32_t *rows, const void 
     return check_pdl_launch(g_launch_err, "dyt");
 }
 
-extern "C" int hfb_dyt_residual(const void *y, int y_dt, int splits, const void *bias, int bias_dt, const void *alpha, const void *w, const void *b, int p_dt,
+extern "C" int hfb_dyt_residual(const void *y, int y_dt, int splits, const void *bias, int bias_dt, const float *mix_y,
+                                const float *mix_w, int top, const void *alpha, const void *w, const void *b, int p_dt,
                                 float *residual, const void *alpha2, const void *w2, const void *b2, int p2_dt,
                                 void *out, int out_dt, int M, int E, hfb_stream s)
 {
     if (M <= 0) return HFB_OK;
     const int has_next = out != nullptr;
-    if (!valid_dt(y_dt) || !valid_dt(p_dt) || E <= 0 || !alpha || !w || !b || !residual || splits < 1 || (bias && !valid_dt(bias_dt)) ||
+    if (!valid_dt(y_dt) || !valid_dt(p_dt) || E <= 0 || !alpha || !w || !b || !residual || splits < 0 || (splits > 0 && !y) ||
+        (bias && !valid_dt(bias_dt)) || (mix_y && (!mix_w || top < 1)) || (!mix_y && splits < 1) ||
         (has_next && (!alpha2 || !w2 || !b2 || !valid_dt(p2_dt) || !valid_dt(out_dt))))
         return fail(HFB_EINVAL, "dyt_residual: bad arguments");
     DytParams p{alpha, w, b, p_dt}, n{alpha2, w2, b2, p2_dt};
     const unsigned blocks = blocks_for((size_t)M * E);
-    if (y_dt == HFB_F32) g_launch_err = launch_pdl(dyt_residual_kernel<float>, dim3(blocks), dim3(256), 0, (cudaStream_t)s, (const float *)y, splits, bias, bias_dt, p, residual, has_next, n, out, out_dt, M, E);
-    else g_launch_err = launch_pdl(dyt_residual_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, (cudaStream_t)s, (const __nv_bfloat16 *)y, splits, bias, bias_dt, p, residual, has_next, n, out, out_dt, M, E);
+    if (y_dt == HFB_F32) g_launch_err = launch_pdl(dyt_residual_kernel<float>, dim3(blocks), dim3(256), 0, (cudaStream_t)s, (const float *)y, splits, bias, bias_dt, mix_y, mix_w, top, p, residual, has_next, n, out, out_dt, M, E);
+    else g_launch_err = launch_pdl(dyt_residual_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, (cudaStream_t)s, (const __nv_bfloat16 *)y, splits, bias, bias_dt, mix_y, mix_w, top, p, residual, has_next, n, out, out_dt, M, E);
     return check_pdl_launch(g_launch_err, "dyt_residual");
 }
 

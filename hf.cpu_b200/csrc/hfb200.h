@@ -160,9 +160,11 @@ int hfb_scale(float *x, int64_t total, float scale, hfb_stream s);
 int hfb_dyt(const void *x, int x_dt, const int32_t *rows, const void *alpha, const void *w, const void *b,
             int p_dt, void *out, int out_dt, int M, int E, hfb_stream s);
 
-/* residual += dyt(y); with out != NULL also out = dyt2(residual) (the next sublayer's input).  y [splits, M, E]: partial
- * sums of a product, summed in order, plus its bias (null: none); a finished y has splits = 1. */
-int hfb_dyt_residual(const void *y, int y_dt, int splits, const void *bias, int bias_dt, const void *alpha, const void *w, const void *b, int p_dt,
+/* residual += dyt(y); with out != NULL also out = dyt2(residual) (the next sublayer's input).  y is the sum, in this
+ * order, of: y [splits, M, E], the partial sums of a product (a finished y has splits = 1; none: splits = 0), the
+ * product's bias (null: none), and sum_j mix_w[m, j] * mix_y[m * top + j, :] (float32; null: none). */
+int hfb_dyt_residual(const void *y, int y_dt, int splits, const void *bias, int bias_dt, const float *mix_y,
+                     const float *mix_w, int top, const void *alpha, const void *w, const void *b, int p_dt,
                      float *residual, const void *alpha2, const void *w2, const void *b2, int p2_dt,
                      void *out, int out_dt, int M, int E, hfb_stream s);
 
@@ -174,9 +176,11 @@ int hfb_rope_norm_kv_write(const float *src, int splits, const void *bias, int b
                            void *q_out, void *k_cache, void *v_cache, int out_dt, int64_t cache_slots, int T,
                            int H, int G, int d, int dv, int norm, float eps, hfb_stream s);
 
-/* The choice of a mixture of experts' router from its float32 logits z [T, E]: the `top` largest (lowest index first
+/* The choice of a mixture of experts' router from its float32 logits z [splits, T, E] (partial sums of the router's
+ * product, summed in order, plus its bias; finished logits: splits = 1, bias null): the `top` largest (lowest index first
  * among equals) go to ids [T, top], their softmax over the chosen logits only to weights [T, top]. */
-int hfb_moe_topk(const float *z, int T, int E, int top, int32_t *ids, float *weights, hfb_stream s);
+int hfb_moe_topk(const float *z, int splits, const void *bias, int bias_dt, int T, int E, int top, int32_t *ids,
+                 float *weights, hfb_stream s);
 
 /* Groups the T * top (token, choice) pairs by expert: order[p] = pair at sorted place p; tiles of at most `tile`
  * places of one expert in tile_expert / tile_p0 / tile_n (room for hfb_moe_max_tiles entries); *n_tiles on the device. */

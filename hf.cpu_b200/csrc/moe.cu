@@ -16,10 +16,12 @@ namespace hfb {
 
 constexpr int ROUTE_WARPS = 4;
 
-// The choice of experts from finished router logits z [T, E] (float32): one warp per token; the `top` largest, the
-// lower index among equals; weights = softmax over the chosen logits only.  smem per warp: E logits, `top` chosen.
+// The choice of experts from the router's logits z [splits, T, E] (float32: partial sums of the router's product,
+// summed in split order, plus its bias; finished logits have one split and no bias): one warp per token; the `top`
+// largest, the lower index among equals; weights = softmax over the chosen logits only.  smem per warp: E logits, `top`
+// chosen.
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
-moe_topk_kernel(const float *zs, int T, int E, int top, int32_t *ids, float *weights)
+moe_topk_kernel(const float *zs, int splits, const void *bias, int bias_dt, int T, int E, int top, int32_t *ids, float *weights)
 {
     pdl_entry();
     pdl_sync_small();
@@ -28,7 +30,11 @@ moe_topk_kernel(const float *zs, int T, int E, int top, int32_t *ids, float *wei
     const int t = blockIdx.x * ROUTE_WARPS + warp;
     if (t >= T) return;
     float *z = route_smem + (size_t)warp * (E + top), *zc = z + E;
-    for (int e = lane; e < E; e += 32) z[e] = zs[(size_t)t * E + e];
+    for (int e = lane; e < E; e += 32) {
+        float v = 0.f;
+        for (int s = 0; s < splits; s++) v += zs[((size_t)s * T + t) * E + e];
+        z[e] = bias ? v + load_any(bias, bias_dt, e) : v;
+    }
     __syncwarp();
     for (int j = 0; j < top; j++) {
         float best = -INFINITY;
@@ -353,13 +359,14 @@ static bool plain_products()
     return v != 0;
 }
 
-extern "C" int hfb_moe_topk(const float *z, int T, int E, int top, int32_t *ids, float *weights, hfb_stream s)
+extern "C" int hfb_moe_topk(const float *z, int splits, const void *bias, int bias_dt, int T, int E, int top, int32_t *ids,
+                            float *weights, hfb_stream s)
 {
     if (T <= 0) return HFB_OK;
-    if (E <= 0 || top <= 0 || top > E) return fail(HFB_EINVAL, "moe_topk: bad arguments (experts=%d top=%d)", E, top);
+    if (E <= 0 || top <= 0 || top > E || splits < 1 || (bias && !valid_dt(bias_dt))) return fail(HFB_EINVAL, "moe_topk: bad arguments (experts=%d top=%d)", E, top);
     const size_t smem = (size_t)ROUTE_WARPS * (E + top) * sizeof(float);
     if (smem > 48 * 1024) return fail(HFB_ENOTSUP, "moe_topk: %d experts are more than the kernel takes", E);
-    g_launch_err = launch_pdl(moe_topk_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, (cudaStream_t)s, z, T, E, top, ids, weights);
+    g_launch_err = launch_pdl(moe_topk_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, (cudaStream_t)s, z, splits, bias, bias_dt, T, E, top, ids, weights);
     return check_pdl_launch(g_launch_err, "moe_topk");
 }
 

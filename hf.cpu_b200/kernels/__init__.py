@@ -233,20 +233,34 @@ def dyt(x: torch.Tensor, params, out: torch.Tensor, rows: Optional[torch.Tensor]
     backend().dyt(x, params, out, rows)
 
 
-def dyt_residual(y: torch.Tensor, post, residual: torch.Tensor, nxt=None, out: Optional[torch.Tensor] = None) -> None:
-    """residual += dyt_post(y); with ``nxt`` and ``out`` also out = dyt_nxt(residual)."""
-    _need(residual.dtype == torch.float32 and y.shape == residual.shape, "dyt_residual: shape mismatch")
-    _dyt_ok(post, y.shape[1], "dyt_residual")
+def _mix_ok(mix, residual, what):
+    if mix is not None:
+        y, w = mix
+        _need(w.dim() == 2 and w.shape[0] == residual.shape[0] and y.shape == (w.shape[0] * w.shape[1], residual.shape[1])
+              and y.dtype == torch.float32 and w.dtype == torch.float32, f"{what}: mix = (float32 [M * top, E], float32 [M, top])")
+
+
+def dyt_residual(y: Optional[torch.Tensor], post, residual: torch.Tensor, nxt=None, out: Optional[torch.Tensor] = None,
+                 mix=None) -> None:
+    """residual += dyt_post(y + mix); with ``nxt`` and ``out`` also out = dyt_nxt(residual).  ``mix`` = (rows [M * top,
+    E], weights [M, top]) adds ``sum_j weights[m, j] * rows[m * top + j]`` (j in order) to y, which may then be None."""
+    _need(residual.dtype == torch.float32 and (y.shape == residual.shape if y is not None else mix is not None), "dyt_residual: shape mismatch")
+    _mix_ok(mix, residual, "dyt_residual")
+    _dyt_ok(post, residual.shape[1], "dyt_residual")
     _need((nxt is None) == (out is None), "dyt_residual: the next norm and its output come together")
     if nxt is not None:
-        _dyt_ok(nxt, y.shape[1], "dyt_residual")
+        _dyt_ok(nxt, residual.shape[1], "dyt_residual")
         _need(out.shape == residual.shape, "dyt_residual: output shape mismatch")
-    backend().dyt_residual(y, post, residual, nxt, out)
+    if mix is None:
+        backend().dyt_residual(y, post, residual, nxt, out)
+    else:
+        backend().dyt_residual(y, post, residual, nxt, out, mix=mix)
 
 
-def linear_dyt_residual(a, w, bias, y_buf, post, residual, nxt=None, out=None) -> None:
-    """residual += dyt_post(a @ w.T + bias), and with ``nxt`` / ``out`` the next norm of the new residual, as
+def linear_dyt_residual(a, w, bias, y_buf, post, residual, nxt=None, out=None, mix=None) -> None:
+    """residual += dyt_post(a @ w.T + bias + mix), and with ``nxt`` / ``out`` the next norm of the new residual, as
     :func:`dyt_residual`; ``y_buf`` [M, N] float32 is scratch for the form that finishes the product first."""
+    _mix_ok(mix, residual, "linear_dyt_residual")
     _need(a.shape[1] == w.shape[1] and residual.shape == (a.shape[0], w.shape[0]) and residual.dtype == torch.float32,
           "linear_dyt_residual: shape mismatch")
     _need(y_buf.shape == residual.shape and y_buf.dtype == torch.float32, "linear_dyt_residual: scratch must be float32 [M, N]")
@@ -255,7 +269,10 @@ def linear_dyt_residual(a, w, bias, y_buf, post, residual, nxt=None, out=None) -
     if nxt is not None:
         _dyt_ok(nxt, w.shape[0], "linear_dyt_residual")
         _need(out.shape == residual.shape, "linear_dyt_residual: output shape mismatch")
-    backend().linear_dyt_residual(a, w, bias, y_buf, post, residual, nxt, out)
+    if mix is None:
+        backend().linear_dyt_residual(a, w, bias, y_buf, post, residual, nxt, out)
+    else:
+        backend().linear_dyt_residual(a, w, bias, y_buf, post, residual, nxt, out, mix=mix)
 
 
 def linear_rope_norm_kv(a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d, dv,

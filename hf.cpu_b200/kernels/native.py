@@ -338,23 +338,27 @@ class NativeBackend:
         self._check(self.lib.hfb_dyt(_p(x), c_int(_dt(x)), _p(rows), _p(alpha), _p(w), _p(b), c_int(_dt(w)), _p(out),
                                      c_int(_dt(out)), c_int(M), c_int(E), self._stream()), "dyt")
 
-    def linear_dyt_residual(self, a, w, bias, y_buf, post, residual, nxt, out):
-        """residual += dyt(a @ w.T + bias): the product's split-K partial sums are summed by the norm's own pass
-        where the product is split, else it stores float32 to ``y_buf`` first."""
+    def linear_dyt_residual(self, a, w, bias, y_buf, post, residual, nxt, out, mix=None):
+        """residual += dyt(a @ w.T + bias (+ mix)): the product's split-K partial sums are summed by the norm's own
+        pass where the product is split, else it stores float32 to ``y_buf`` first."""
         self._on_gpu(a, w, bias, y_buf)
         part = self._partials(a, w) if self._tc_ok(a, w) else None
         if part is None:
             self.linear(a, w, bias, y_buf, False)
-            self.dyt_residual(y_buf, post, residual, nxt, out)
+            self.dyt_residual(y_buf, post, residual, nxt, out, mix=mix)
         else:
-            self.dyt_residual(part[0], post, residual, nxt, out, splits=part[1], bias=bias, as_f32=True)
+            self.dyt_residual(part[0], post, residual, nxt, out, splits=part[1], bias=bias, as_f32=True, mix=mix)
 
-    def dyt_residual(self, y, post, residual, nxt, out, splits=1, bias=None, as_f32=False):
-        self._on_gpu(*post, residual, out, *(nxt or ()))
+    def dyt_residual(self, y, post, residual, nxt, out, splits=1, bias=None, as_f32=False, mix=None):
+        self._on_gpu(*post, residual, out, *(nxt or ()), *(mix or ()))
         M, E = residual.shape
         n = nxt or (None, None, None)
+        if y is None:
+            splits = 0
+        mix_y, mix_w = mix or (None, None)
         self._check(self.lib.hfb_dyt_residual(
-            _p(y), c_int(F32 if as_f32 else _dt(y)), c_int(splits), _p(bias), c_int(_dt(bias) if bias is not None else 0), _p(post[0]), _p(post[1]), _p(post[2]), c_int(_dt(post[1])), _p(residual), _p(n[0]), _p(n[1]),
+            _p(y), c_int(F32 if as_f32 or y is None else _dt(y)), c_int(splits), _p(bias), c_int(_dt(bias) if bias is not None else 0),
+            _p(mix_y), _p(mix_w), c_int(mix_w.shape[1] if mix_w is not None else 0), _p(post[0]), _p(post[1]), _p(post[2]), c_int(_dt(post[1])), _p(residual), _p(n[0]), _p(n[1]),
             _p(n[2]), c_int(_dt(n[1]) if nxt else 0), _p(out), c_int(_dt(out) if out is not None else 0), c_int(M), c_int(E),
             self._stream()), "dyt_residual")
 
@@ -404,10 +408,15 @@ class NativeBackend:
 
     def moe_route(self, h, w, b, top, ids, weights, logits):
         self._on_gpu(h, w, b, ids, weights, logits)
-        self.linear(h, w, b, logits, False)
         T, E = logits.shape
-        self._check(self.lib.hfb_moe_topk(_p(logits), c_int(T), c_int(E), c_int(top), _p(ids), _p(weights), self._stream()),
-                    "moe_topk")
+        part = self._partials(h, w) if self._tc_ok(h, w) else None
+        if part is None:
+            self.linear(h, w, b, logits, False)
+            src, splits, b = logits, 1, None
+        else:                                   # the top-k kernel sums the product's partial sums itself
+            src, splits = part
+        self._check(self.lib.hfb_moe_topk(_p(src), c_int(splits), _p(b), c_int(_dt(b) if b is not None else 0), c_int(T), c_int(E),
+                                          c_int(top), _p(ids), _p(weights), self._stream()), "moe_topk")
 
     def moe_group(self, ids, experts, order, tile_expert, tile_p0, tile_n, n_tiles):
         self._on_gpu(ids, order, tile_expert, tile_p0, tile_n, n_tiles)

@@ -71,7 +71,8 @@ class MoeFfn(FeedForward):
     def flops(self, rows):
         return 2.0 * rows * (self.n * self.E + 2 * self.top * self.E * self.F + 2 * self.E * self.FS)
 
-    def forward(self, ctx, xn, residual, accumulate=True):
+    def _experts(self, ctx, xn):
+        """Router, grouping and the routed experts: (outputs of every (token, choice) [T * top, E] float32, weights [T, top])."""
         T, P = xn.shape[0], xn.shape[0] * self.top
         i32 = torch.int32
         ids = ctx.buf("moe_ids", (T, self.top), i32)
@@ -90,15 +91,34 @@ class MoeFfn(FeedForward):
             kernels.moe_gemm(xn, self.w_up, h, self.activation, order, self.top, False, *tiles, n_tiles, P)
         with kernels.phase("down"):
             kernels.moe_gemm(h, self.w_down, y, "none", order, 0, True, *tiles, n_tiles, P)
+        return y, wts
+
+    def _shared_hidden(self, ctx, xn):
+        hs = ctx.buf("moe_hs", (xn.shape[0], self.FS), xn.dtype)
+        with kernels.phase("gate_up"):
+            kernels.linear_act(xn, self.ws_up, hs, self.activation)
+        return hs
+
+    def forward_into_norm(self, ctx, xn, y_buf, residual, post, next_norm, out):
+        """residual += post(feed-forward output): the weighted sum of the chosen experts, the shared expert's down
+        product and its partial sums are all summed by the norm's own pass."""
+        mix = self._experts(ctx, xn)
+        if not self.FS:
+            return post.add_into(None, residual, next_norm, out, mix=mix)
+        hs = self._shared_hidden(ctx, xn)
+        with kernels.phase("down"):
+            return post.add_product_into(hs, self.ws_down, None, y_buf, residual, next_norm, out, mix=mix)
+
+    def forward(self, ctx, xn, residual, accumulate=True):
+        T = xn.shape[0]
+        y, wts = self._experts(ctx, xn)
         out = residual
         if accumulate:
             out = ctx.buf("moe_out", residual.shape, torch.float32)
         with kernels.phase("glue"):
             kernels.moe_combine(y, wts, out)
         if self.FS:
-            hs = ctx.buf("moe_hs", (T, self.FS), xn.dtype)
-            with kernels.phase("gate_up"):
-                kernels.linear_act(xn, self.ws_up, hs, self.activation)
+            hs = self._shared_hidden(ctx, xn)
             with kernels.phase("down"):
                 kernels.linear(hs, self.ws_down, None, out, accumulate=True)
         if accumulate:

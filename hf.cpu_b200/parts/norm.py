@@ -60,20 +60,21 @@ class DynamicTanh(Norm):
             kernels.dyt(x, self.params, out, rows)
         return out
 
-    def add_into(self, y, residual, next_norm=None, out=None):
+    def add_into(self, y, residual, next_norm=None, out=None, mix=None):
         """residual += norm(y); when ``next_norm`` is another Dynamic Tanh, ``out = next_norm(residual)`` comes out of
-        the same pass.  Returns whether ``out`` was written."""
+        the same pass.  Returns whether ``out`` was written.  ``mix`` = (rows, weights) adds a weighted sum of rows per
+        token to y (a routed feed-forward's chosen experts), summed by the same pass; y may then be None."""
         fused = out is not None and isinstance(next_norm, DynamicTanh)
         with kernels.phase("glue"):
-            kernels.dyt_residual(y, self.params, residual, next_norm.params if fused else None, out if fused else None)
+            kernels.dyt_residual(y, self.params, residual, next_norm.params if fused else None, out if fused else None, mix=mix)
         return fused
 
-    def add_product_into(self, a, w, bias, y_buf, residual, next_norm=None, out=None):
-        """The same for a sublayer whose output is a product, ``a @ w.T + bias``: where the product is split over its
-        inner dimension, the partial sums are summed by this norm's own pass."""
+    def add_product_into(self, a, w, bias, y_buf, residual, next_norm=None, out=None, mix=None):
+        """The same for a sublayer whose output is a product, ``a @ w.T + bias (+ mix)``: where the product is split over
+        its inner dimension, the partial sums are summed by this norm's own pass."""
         fused = out is not None and isinstance(next_norm, DynamicTanh)
         kernels.linear_dyt_residual(a, w, bias, y_buf, self.params, residual, next_norm.params if fused else None,
-                                    out if fused else None)
+                                    out if fused else None, mix=mix)
         return fused
 
 

@@ -104,14 +104,18 @@ class EmuBackend:
         xr = x if rows is None else x[rows.long()]
         out.copy_(self._dyt(xr, params).to(out.dtype))
 
-    def dyt_residual(self, y, post, residual, nxt, out):
-        residual.add_(self._dyt(y, post))
+    def dyt_residual(self, y, post, residual, nxt, out, mix=None):
+        v = y.float() if y is not None else torch.zeros_like(residual)
+        if mix is not None:
+            rows, w = mix
+            v = v + (w[:, :, None] * rows.view(w.shape[0], w.shape[1], -1)).sum(1)
+        residual.add_(self._dyt(v, post))
         if nxt is not None:
             out.copy_(self._dyt(residual, nxt).to(out.dtype))
 
-    def linear_dyt_residual(self, a, w, bias, y_buf, post, residual, nxt, out):
+    def linear_dyt_residual(self, a, w, bias, y_buf, post, residual, nxt, out, mix=None):
         self.linear(a, w, bias, y_buf, False)
-        self.dyt_residual(y_buf, post, residual, nxt, out)
+        self.dyt_residual(y_buf, post, residual, nxt, out, mix=mix)
 
     def linear_rope_norm_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d, dv,
                             norm_eps):
