@@ -202,7 +202,8 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *p)
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
-constexpr int MSTAGES = 3;
+// Stages of the tensor-core form: three where tiles are full (two blocks an SM), six for steps of a few tokens, whose
+// blocks only stream their slice of the expert's weights and need more of it in flight (one block an SM).
 
 __device__ __forceinline__ void cp_async_16(void *smem, const void *gmem, bool valid)
 {
@@ -215,13 +216,15 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 constexpr int MN = 128;                                       // features per tile of the tensor-core form
-constexpr size_t MMA_SMEM = (size_t)MSTAGES * (MT + MN) * (MK + MPAD) * sizeof(__nv_bfloat16) + 2 * MT * sizeof(int);
+template <int MSTAGES> constexpr size_t mma_smem() { return (size_t)MSTAGES * (MT + MN) * (MK + MPAD) * sizeof(__nv_bfloat16) + 2 * MT * sizeof(int); }
 
+template <int MSTAGES>
 __global__ void __launch_bounds__(256)
 moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__restrict__ w, void *out, int out_dt, int act,
                     int N, int K, const int32_t *order, int src_div, int scatter, const int32_t *tile_expert,
-                    const int32_t *tile_p0, const int32_t *tile_n, const int32_t *n_tiles)
+                    const int32_t *tile_p0, const int32_t *tile_n, const int32_t *n_tiles, int nfeat)
 {
+    // nfeat: the features this block owns (MN; with fewer the rest of the tile is zeros and the grid has more blocks)
     pdl_sync();
     const int ti = blockIdx.y;
     if (ti >= *n_tiles) return;
@@ -232,7 +235,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
     auto sa = [&](int st) { return (Stage)(sa_base + (size_t)st * MT * (MK + MPAD)); };
     auto sw = [&](int st) { return (Stage)(sw_base + (size_t)st * MN * (MK + MPAD)); };
     const int e = tile_expert[ti], p0 = tile_p0[ti], rows = tile_n[ti];
-    const int n0 = blockIdx.x * MN;
+    const int n0 = blockIdx.x * nfeat, n_end = min(N, n0 + nfeat);
     if (threadIdx.x < MT) {
         const int r = threadIdx.x;
         int src = -1, dst = -1;
@@ -256,7 +259,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
     for (int i = 0; i < 2; i++) {
         const int src = s_src[vr + 64 * i], gn = n0 + vr + 64 * i;
         pa[i] = src >= 0 ? a + (size_t)src * K + vk : nullptr;
-        pw[i] = gn < N ? we + (size_t)gn * K + vk : nullptr;
+        pw[i] = gn < n_end ? we + (size_t)gn * K + vk : nullptr;
     }
     // a piece of k on its way into stage `st` (rows that do not exist and k beyond K arrive as zeros)
     auto fetch = [&](int k0, int st) {
@@ -278,15 +281,16 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
     const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
     const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
     const int chunks = (K + MK - 1) / MK;
-    fetch(0, 0);
-    cp_async_commit();
-    if (chunks > 1) fetch(MK, 1);
-    cp_async_commit();
+#pragma unroll
+    for (int c = 0; c < MSTAGES - 1; c++) {
+        if (c < chunks) fetch(c * MK, c);
+        cp_async_commit();
+    }
     for (int c = 0; c < chunks; c++) {
         const int st = c % MSTAGES;
-        cp_async_wait<1>();                      // piece c has landed (one newer group may still be in flight)
+        cp_async_wait<MSTAGES - 2>();            // piece c has landed (the newer groups may still be in flight)
         __syncthreads();                         // ... for every thread, and piece c - 1 has been multiplied by all
-        if (c + 2 < chunks) fetch((c + 2) * MK, (c + 2) % MSTAGES);
+        if (c + MSTAGES - 1 < chunks) fetch((c + MSTAGES - 1) * MK, (c + MSTAGES - 1) % MSTAGES);
         cp_async_commit();
         if (live0) {
 #pragma unroll
@@ -320,7 +324,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
 #pragma unroll
                 for (int j = 0; j < 2; j++) {
                     const int gn = n0 + 64 * wn + nt * 8 + 2 * t + j;
-                    if (gn >= N) continue;
+                    if (gn >= n_end) continue;
                     float v = acc[m][nt][2 * half + j];
                     if (act == HFB_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
                     else if (act == HFB_ACT_RELU) v = fmaxf(v, 0.f);
@@ -389,9 +393,10 @@ extern "C" int hfb_moe_sort(const int32_t *ids, int pairs, int E, int tile, int3
 
 extern "C" int hfb_moe_gemm(const void *a, int a_dt, const void *w, int w_dt, void *out, int out_dt, int act, int N, int K,
                             const int32_t *order, int src_div, int scatter, const int32_t *tile_expert, const int32_t *tile_p0,
-                            const int32_t *tile_n, const int32_t *n_tiles, int max_tiles, int tile, hfb_stream s)
+                            const int32_t *tile_n, const int32_t *n_tiles, int max_tiles, int tile, int places, hfb_stream s)
 {
     if (max_tiles <= 0) return HFB_OK;
+    const bool deep = places > 0 && places <= 512;
     if (!valid_dt(a_dt) || !valid_dt(w_dt) || !valid_dt(out_dt) || N <= 0 || K <= 0 || tile != MT || act < 0 || act > HFB_ACT_NONE)
         return fail(HFB_EINVAL, "moe_gemm: bad arguments (N=%d K=%d tile=%d)", N, K, tile);
     if (max_tiles > 65535) return fail(HFB_ENOTSUP, "moe_gemm: %d tiles exceed the grid", max_tiles);
@@ -402,12 +407,18 @@ extern "C" int hfb_moe_gemm(const void *a, int a_dt, const void *w, int w_dt, vo
         static bool opted[64] = {};              // more than 48 KB of shared memory: asked for once per device
         const int dev = current_device();
         if (!opted[dev]) {
-            if (cudaFuncSetAttribute(moe_gemm_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM) != cudaSuccess)
+            if (cudaFuncSetAttribute(moe_gemm_mma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mma_smem<3>()) != cudaSuccess ||
+                cudaFuncSetAttribute(moe_gemm_mma_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mma_smem<6>()) != cudaSuccess)
                 return fail(HFB_ECUDA, "moe_gemm: the kernel's shared memory could not be set");
             opted[dev] = true;
         }
-        g_launch_err = launch_pdl(moe_gemm_mma_kernel, dim3((N + MN - 1) / MN, max_tiles), dim3(256), MMA_SMEM, st, (const __nv_bfloat16 *)a, (const __nv_bfloat16 *)w, out, out_dt, act, N, K,
-                                  order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles);
+        // the tiles of a step of few tokens hold a handful of places each: its blocks stream weights and little else
+        if (deep)
+            g_launch_err = launch_pdl(moe_gemm_mma_kernel<6>, dim3((N + MN - 1) / MN, max_tiles), dim3(256), mma_smem<6>(), st, (const __nv_bfloat16 *)a, (const __nv_bfloat16 *)w, out, out_dt, act, N, K,
+                                      order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles, MN);
+        else
+        g_launch_err = launch_pdl(moe_gemm_mma_kernel<3>, dim3((N + MN - 1) / MN, max_tiles), dim3(256), mma_smem<3>(), st, (const __nv_bfloat16 *)a, (const __nv_bfloat16 *)w, out, out_dt, act, N, K,
+                                  order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles, MN);
         return check_pdl_launch(g_launch_err, "moe_gemm_mma");
     }
 #define LAUNCH(TA, TW) g_launch_err = launch_pdl(moe_gemm_kernel<TA, TW>, dim3(grid.x, grid.y, MT / GT), dim3(256), 0, st, (const TA *)a, (const TW *)w, out, out_dt, act, N, K, order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles)

@@ -346,7 +346,7 @@ def moe_gemm(a, w, out, act: str, order, src_div: int, scatter: bool, tile_exper
     w [E, N, K]; src(p) = order[p] // src_div if src_div else p; dst(p) = order[p] if scatter else p."""
     _need(w.dim() == 3 and a.shape[1] == w.shape[2] and out.shape[1] == w.shape[1], "moe_gemm: shape mismatch")
     backend().moe_gemm(a, w, out, _act(act), order, int(src_div), bool(scatter), tile_expert, tile_p0, tile_n, n_tiles,
-                       moe_max_tiles(int(pairs), w.shape[0]))
+                       moe_max_tiles(int(pairs), w.shape[0]), int(pairs))
 
 
 def moe_combine(y, weights, out) -> None:

@@ -187,7 +187,7 @@ class EmuBackend:
             at += c
         n_tiles[0] = n
 
-    def moe_gemm(self, a, w, out, act, order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles, max_tiles):
+    def moe_gemm(self, a, w, out, act, order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles, max_tiles, places=0):
         assert int(n_tiles[0]) <= max_tiles
         for i in range(int(n_tiles[0])):
             e, p0, n = int(tile_expert[i]), int(tile_p0[i]), int(tile_n[i])
