@@ -183,17 +183,18 @@ int hfb_moe_topk(const float *z, int splits, const void *bias, int bias_dt, int 
                  float *weights, hfb_stream s);
 
 /* Groups the T * top (token, choice) pairs by expert: order[p] = pair at sorted place p; tiles of at most `tile`
- * places of one expert in tile_expert / tile_p0 / tile_n (room for hfb_moe_max_tiles entries); *n_tiles on the device. */
+ * places of one expert in tile_expert / tile_p0 / tile_n (room for hfb_moe_max_tiles entries); *n_tiles on the device.
+ * Steps of few tokens ask for tiles of 16 places (more, smaller blocks for the product behind). */
 int hfb_moe_max_tiles(int pairs, int E, int tile);
 int hfb_moe_sort(const int32_t *ids, int pairs, int E, int tile, int32_t *order, int32_t *tile_expert, int32_t *tile_p0,
                  int32_t *tile_n, int32_t *n_tiles, hfb_stream s);
 
 /* Grouped product over the sorted places: out[dst(p), :] = act(a[src(p), :] . w[expert(p)]^T), w [E, N, K].
- * src(p) = order[p] / src_div when src_div > 0, else p; dst(p) = order[p] when scatter != 0, else p.  `places` (all the
- * lists hold; 0: unknown) picks the form for steps of few tokens. */
+ * src(p) = order[p] / src_div when src_div > 0, else p; dst(p) = order[p] when scatter != 0, else p.  `tile`: the most
+ * places a tile of the lists holds, up to 128; with 16 and less the form for steps of a few tokens runs. */
 int hfb_moe_gemm(const void *a, int a_dt, const void *w, int w_dt, void *out, int out_dt, int act, int N, int K,
                  const int32_t *order, int src_div, int scatter, const int32_t *tile_expert, const int32_t *tile_p0,
-                 const int32_t *tile_n, const int32_t *n_tiles, int max_tiles, int tile, int places, hfb_stream s);
+                 const int32_t *tile_n, const int32_t *n_tiles, int max_tiles, int tile, hfb_stream s);
 
 /* out[t, :] = sum_j weights[t, j] * y[t * top + j, :] in float32, j in order */
 int hfb_moe_combine(const void *y, int y_dt, const float *weights, float *out, int T, int top, int N, hfb_stream s);

@@ -183,9 +183,9 @@ moe_gemm_kernel(const TA *__restrict__ a, const TW *__restrict__ w, void *out, i
 // The same grouped product for bfloat16 operands on the tensor cores (mma.sync m16n8k16, float32 accumulators): a tile
 // of 128 places x 128 features, eight warps of 32 places x 64 features each; operands come into padded shared memory
 // by cp.async, 32 of k at a time in three stages, so that two pieces are on their way while one is multiplied;
-// fragments come out of shared memory with ldmatrix.x4.  A warp whose places lie beyond the tile's count multiplies nothing (a step of single
-// tokens has a handful of places per expert).  K is a multiple of 8 and the operands are 16-byte aligned (every
-// 16-byte piece of a row lies wholly inside or outside K).
+// fragments come out of shared memory with ldmatrix.x4.  A warp whose places lie beyond the tile's count multiplies
+// nothing.  K is a multiple of 8 and the operands are 16-byte aligned (every 16-byte piece of a row lies wholly inside
+// or outside K).
 constexpr int MT = 128, MK = 32, MPAD = 8;
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
@@ -202,8 +202,7 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *p)
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
-// Stages of the tensor-core form: three where tiles are full (two blocks an SM), six for steps of a few tokens, whose
-// blocks only stream their slice of the expert's weights and need more of it in flight (one block an SM).
+constexpr int MSTAGES = 3;
 
 __device__ __forceinline__ void cp_async_16(void *smem, const void *gmem, bool valid)
 {
@@ -216,15 +215,13 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 constexpr int MN = 128;                                       // features per tile of the tensor-core form
-template <int MSTAGES> constexpr size_t mma_smem() { return (size_t)MSTAGES * (MT + MN) * (MK + MPAD) * sizeof(__nv_bfloat16) + 2 * MT * sizeof(int); }
+constexpr size_t MMA_SMEM = (size_t)MSTAGES * (MT + MN) * (MK + MPAD) * sizeof(__nv_bfloat16) + 2 * MT * sizeof(int);
 
-template <int MSTAGES>
 __global__ void __launch_bounds__(256)
 moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__restrict__ w, void *out, int out_dt, int act,
                     int N, int K, const int32_t *order, int src_div, int scatter, const int32_t *tile_expert,
-                    const int32_t *tile_p0, const int32_t *tile_n, const int32_t *n_tiles, int nfeat)
+                    const int32_t *tile_p0, const int32_t *tile_n, const int32_t *n_tiles)
 {
-    // nfeat: the features this block owns (MN; with fewer the rest of the tile is zeros and the grid has more blocks)
     pdl_sync();
     const int ti = blockIdx.y;
     if (ti >= *n_tiles) return;
@@ -235,7 +232,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
     auto sa = [&](int st) { return (Stage)(sa_base + (size_t)st * MT * (MK + MPAD)); };
     auto sw = [&](int st) { return (Stage)(sw_base + (size_t)st * MN * (MK + MPAD)); };
     const int e = tile_expert[ti], p0 = tile_p0[ti], rows = tile_n[ti];
-    const int n0 = blockIdx.x * nfeat, n_end = min(N, n0 + nfeat);
+    const int n0 = blockIdx.x * MN, n_end = min(N, n0 + MN);
     if (threadIdx.x < MT) {
         const int r = threadIdx.x;
         int src = -1, dst = -1;
@@ -337,6 +334,108 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
     }
 }
 
+// The form for steps of a few tokens, whose tiles hold at most 16 places (the grouping is asked for tiles of 16): a
+// block only streams its slice of an expert's weights, so slices are narrow (64 features: many blocks, spread evenly
+// over the SMs), pieces are long (64 of k) and many are in flight (eight stages, two blocks an SM).  Four warps, each
+// 16 places x 16 features.
+constexpr int ST_ROWS = 16, ST_N = 64, ST_K = 64, ST_STAGES = 8;
+constexpr size_t SMALL_SMEM = (size_t)ST_STAGES * (ST_ROWS + ST_N) * (ST_K + MPAD) * sizeof(__nv_bfloat16);
+
+__global__ void __launch_bounds__(128)
+moe_gemm_small_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__restrict__ w, void *out, int out_dt, int act,
+                      int N, int K, const int32_t *order, int src_div, int scatter, const int32_t *tile_expert,
+                      const int32_t *tile_p0, const int32_t *tile_n, const int32_t *n_tiles)
+{
+    pdl_sync();
+    const int ti = blockIdx.y;
+    if (ti >= *n_tiles) return;
+    extern __shared__ __align__(16) uint8_t small_smem[];
+    typedef __nv_bfloat16 (*Stage)[ST_K + MPAD];
+    __nv_bfloat16 *sa_base = (__nv_bfloat16 *)small_smem, *sw_base = sa_base + (size_t)ST_STAGES * ST_ROWS * (ST_K + MPAD);
+    auto sa = [&](int st) { return (Stage)(sa_base + (size_t)st * ST_ROWS * (ST_K + MPAD)); };
+    auto sw = [&](int st) { return (Stage)(sw_base + (size_t)st * ST_N * (ST_K + MPAD)); };
+    __shared__ int s_src[ST_ROWS], s_dst[ST_ROWS];
+    const int e = tile_expert[ti], p0 = tile_p0[ti], rows = min(tile_n[ti], ST_ROWS);
+    const int n0 = blockIdx.x * ST_N;
+    if (threadIdx.x < ST_ROWS) {
+        const int r = threadIdx.x;
+        int src = -1, dst = -1;
+        if (r < rows) {
+            const int p = p0 + r, pair = order[p];
+            src = src_div > 0 ? pair / src_div : p;
+            dst = scatter ? pair : p;
+        }
+        s_src[r] = src;
+        s_dst[r] = dst;
+    }
+    __syncthreads();
+    const __nv_bfloat16 *we = w + (size_t)e * N * K;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    // the 16-byte pieces this thread moves per 64 of k: one of a place's row, four of the weights' rows
+    const int vk = (threadIdx.x & 7) * 8, ar = threadIdx.x >> 3, wr = threadIdx.x >> 3;
+    const int asrc = s_src[ar];
+    const __nv_bfloat16 *pa = asrc >= 0 ? a + (size_t)asrc * K + vk : nullptr, *pw[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int gn = n0 + wr + 16 * i;
+        pw[i] = gn < N ? we + (size_t)gn * K + vk : nullptr;
+    }
+    auto fetch = [&](int k0, int st) {
+        const bool in = k0 + vk < K;
+        cp_async_16(&sa(st)[ar][vk], pa && in ? pa + k0 : a, pa && in);
+#pragma unroll
+        for (int i = 0; i < 4; i++) cp_async_16(&sw(st)[wr + 16 * i][vk], pw[i] && in ? pw[i] + k0 : w, pw[i] && in);
+    };
+    float acc[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
+    const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
+    const int chunks = (K + ST_K - 1) / ST_K;
+#pragma unroll
+    for (int c = 0; c < ST_STAGES - 1; c++) {
+        if (c < chunks) fetch(c * ST_K, c);
+        cp_async_commit();
+    }
+    for (int c = 0; c < chunks; c++) {
+        const int st = c % ST_STAGES;
+        cp_async_wait<ST_STAGES - 2>();
+        __syncthreads();
+        if (c + ST_STAGES - 1 < chunks) fetch((c + ST_STAGES - 1) * ST_K, (c + ST_STAGES - 1) % ST_STAGES);
+        cp_async_commit();
+#pragma unroll
+        for (int ks = 0; ks < ST_K; ks += 16) {
+            uint32_t af[4], bf[4];
+            ldmatrix_x4(af, &sa(st)[a_row][ks + a_col]);
+            ldmatrix_x4(bf, &sw(st)[16 * warp + b_row][ks + b_col]);
+            mma_bf16(acc[0], af, bf[0], bf[1]);
+            mma_bf16(acc[1], af, bf[2], bf[3]);
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        const int dst = s_dst[g + 8 * half];
+        if (dst < 0) continue;
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int gn = n0 + 16 * warp + nt * 8 + 2 * t + j;
+                if (gn >= N) continue;
+                float v = acc[nt][2 * half + j];
+                if (act == HFB_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
+                else if (act == HFB_ACT_RELU) v = fmaxf(v, 0.f);
+                else if (act == HFB_ACT_SILU) v = v / (1.0f + expf(-v));
+                else if (act == HFB_ACT_GELU_TANH) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+                store_any(out, out_dt, (size_t)dst * N + gn, v);
+            }
+        }
+    }
+}
+
 template <typename TY>
 __global__ void moe_combine_kernel(const TY *y, const float *weights, float *out, int T, int top, int N)
 {
@@ -393,11 +492,10 @@ extern "C" int hfb_moe_sort(const int32_t *ids, int pairs, int E, int tile, int3
 
 extern "C" int hfb_moe_gemm(const void *a, int a_dt, const void *w, int w_dt, void *out, int out_dt, int act, int N, int K,
                             const int32_t *order, int src_div, int scatter, const int32_t *tile_expert, const int32_t *tile_p0,
-                            const int32_t *tile_n, const int32_t *n_tiles, int max_tiles, int tile, int places, hfb_stream s)
+                            const int32_t *tile_n, const int32_t *n_tiles, int max_tiles, int tile, hfb_stream s)
 {
     if (max_tiles <= 0) return HFB_OK;
-    const bool deep = places > 0 && places <= 512;
-    if (!valid_dt(a_dt) || !valid_dt(w_dt) || !valid_dt(out_dt) || N <= 0 || K <= 0 || tile != MT || act < 0 || act > HFB_ACT_NONE)
+    if (!valid_dt(a_dt) || !valid_dt(w_dt) || !valid_dt(out_dt) || N <= 0 || K <= 0 || tile < 1 || tile > MT || act < 0 || act > HFB_ACT_NONE)
         return fail(HFB_EINVAL, "moe_gemm: bad arguments (N=%d K=%d tile=%d)", N, K, tile);
     if (max_tiles > 65535) return fail(HFB_ENOTSUP, "moe_gemm: %d tiles exceed the grid", max_tiles);
     const dim3 grid((N + GT - 1) / GT, max_tiles);
@@ -407,21 +505,21 @@ extern "C" int hfb_moe_gemm(const void *a, int a_dt, const void *w, int w_dt, vo
         static bool opted[64] = {};              // more than 48 KB of shared memory: asked for once per device
         const int dev = current_device();
         if (!opted[dev]) {
-            if (cudaFuncSetAttribute(moe_gemm_mma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mma_smem<3>()) != cudaSuccess ||
-                cudaFuncSetAttribute(moe_gemm_mma_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mma_smem<6>()) != cudaSuccess)
+            if (cudaFuncSetAttribute(moe_gemm_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMALL_SMEM) != cudaSuccess ||
+                cudaFuncSetAttribute(moe_gemm_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM) != cudaSuccess)
                 return fail(HFB_ECUDA, "moe_gemm: the kernel's shared memory could not be set");
             opted[dev] = true;
         }
-        // the tiles of a step of few tokens hold a handful of places each: its blocks stream weights and little else
-        if (deep)
-            g_launch_err = launch_pdl(moe_gemm_mma_kernel<6>, dim3((N + MN - 1) / MN, max_tiles), dim3(256), mma_smem<6>(), st, (const __nv_bfloat16 *)a, (const __nv_bfloat16 *)w, out, out_dt, act, N, K,
-                                      order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles, MN);
-        else
-        g_launch_err = launch_pdl(moe_gemm_mma_kernel<3>, dim3((N + MN - 1) / MN, max_tiles), dim3(256), mma_smem<3>(), st, (const __nv_bfloat16 *)a, (const __nv_bfloat16 *)w, out, out_dt, act, N, K,
-                                  order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles, MN);
+        if (tile <= ST_ROWS) {                  // tiles of at most 16 places: the form for steps of a few tokens
+            g_launch_err = launch_pdl(moe_gemm_small_kernel, dim3((N + ST_N - 1) / ST_N, max_tiles), dim3(128), SMALL_SMEM, st, (const __nv_bfloat16 *)a,
+                                      (const __nv_bfloat16 *)w, out, out_dt, act, N, K, order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles);
+            return check_pdl_launch(g_launch_err, "moe_gemm_small");
+        }
+        g_launch_err = launch_pdl(moe_gemm_mma_kernel, dim3((N + MN - 1) / MN, max_tiles), dim3(256), MMA_SMEM, st, (const __nv_bfloat16 *)a, (const __nv_bfloat16 *)w, out, out_dt, act, N, K,
+                                  order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles);
         return check_pdl_launch(g_launch_err, "moe_gemm_mma");
     }
-#define LAUNCH(TA, TW) g_launch_err = launch_pdl(moe_gemm_kernel<TA, TW>, dim3(grid.x, grid.y, MT / GT), dim3(256), 0, st, (const TA *)a, (const TW *)w, out, out_dt, act, N, K, order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles)
+#define LAUNCH(TA, TW) g_launch_err = launch_pdl(moe_gemm_kernel<TA, TW>, dim3(grid.x, grid.y, (tile + GT - 1) / GT), dim3(256), 0, st, (const TA *)a, (const TW *)w, out, out_dt, act, N, K, order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles)
     if (a_dt == HFB_F32 && w_dt == HFB_F32) LAUNCH(float, float);
     else if (a_dt == HFB_F32) LAUNCH(float, __nv_bfloat16);
     else if (w_dt == HFB_F32) LAUNCH(__nv_bfloat16, float);

@@ -208,7 +208,14 @@ def linear_rope_kv(a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out,
 
 
 ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "relu2": 3, "none": 4}       # relu2: the square of relu
-MOE_TILE = 128              # places of one expert per tile of the grouped product
+MOE_TILE = 128              # places of one expert per tile of the grouped product ...
+MOE_TILE_FEW = 16           # ... and in steps of few tokens, whose blocks only stream weights: more, smaller tiles
+
+
+def moe_tile(pairs: int) -> int:
+    """Places per tile for a step with ``pairs`` (token, choice) pairs."""
+    return MOE_TILE_FEW if pairs <= 512 else MOE_TILE
+
 
 
 def _act(name: str) -> int:
@@ -327,18 +334,18 @@ def moe_route(h, w, b, top: int, ids, weights, logits) -> None:
     backend().moe_route(h, w, b, int(top), ids, weights, logits)
 
 
-def moe_max_tiles(pairs: int, experts: int) -> int:
+def moe_max_tiles(pairs: int, experts: int, tile: int = 0) -> int:
     """Room for the tile lists of :func:`moe_group`: no grouping of ``pairs`` places over ``experts`` has more tiles."""
-    return pairs // MOE_TILE + min(experts, pairs)
+    return pairs // (tile or moe_tile(pairs)) + min(experts, pairs)
 
 
 def moe_group(ids, experts: int, order, tile_expert, tile_p0, tile_n, n_tiles) -> None:
     """Groups the (token, choice) pairs of ``ids`` [T, top] by expert, on the device: ``order[p]`` = the pair at
-    place p; tiles of at most MOE_TILE places of one expert; their number in ``n_tiles`` [1]."""
+    place p; tiles of at most ``moe_tile(pairs)`` places of one expert; their number in ``n_tiles`` [1]."""
     pairs = ids.numel()
     _need(order.numel() >= pairs and min(tile_expert.numel(), tile_p0.numel(), tile_n.numel()) >= moe_max_tiles(pairs, experts)
           and n_tiles.numel() >= 1, "moe_group: lists too short")
-    backend().moe_group(ids, int(experts), order, tile_expert, tile_p0, tile_n, n_tiles)
+    backend().moe_group(ids, int(experts), order, tile_expert, tile_p0, tile_n, n_tiles, moe_tile(pairs))
 
 
 def moe_gemm(a, w, out, act: str, order, src_div: int, scatter: bool, tile_expert, tile_p0, tile_n, n_tiles, pairs: int) -> None:
@@ -346,7 +353,7 @@ def moe_gemm(a, w, out, act: str, order, src_div: int, scatter: bool, tile_exper
     w [E, N, K]; src(p) = order[p] // src_div if src_div else p; dst(p) = order[p] if scatter else p."""
     _need(w.dim() == 3 and a.shape[1] == w.shape[2] and out.shape[1] == w.shape[1], "moe_gemm: shape mismatch")
     backend().moe_gemm(a, w, out, _act(act), order, int(src_div), bool(scatter), tile_expert, tile_p0, tile_n, n_tiles,
-                       moe_max_tiles(int(pairs), w.shape[0]), int(pairs))
+                       moe_max_tiles(int(pairs), w.shape[0]), moe_tile(int(pairs)))
 
 
 def moe_combine(y, weights, out) -> None:

@@ -418,19 +418,18 @@ class NativeBackend:
         self._check(self.lib.hfb_moe_topk(_p(src), c_int(splits), _p(b), c_int(_dt(b) if b is not None else 0), c_int(T), c_int(E),
                                           c_int(top), _p(ids), _p(weights), self._stream()), "moe_topk")
 
-    def moe_group(self, ids, experts, order, tile_expert, tile_p0, tile_n, n_tiles):
+    def moe_group(self, ids, experts, order, tile_expert, tile_p0, tile_n, n_tiles, tile):
         self._on_gpu(ids, order, tile_expert, tile_p0, tile_n, n_tiles)
-        from . import MOE_TILE
-        self._check(self.lib.hfb_moe_sort(_p(ids), c_int(ids.numel()), c_int(experts), c_int(MOE_TILE), _p(order), _p(tile_expert),
+        self._check(self.lib.hfb_moe_sort(_p(ids), c_int(ids.numel()), c_int(experts), c_int(tile), _p(order), _p(tile_expert),
                                           _p(tile_p0), _p(tile_n), _p(n_tiles), self._stream()), "moe_sort")
 
-    def moe_gemm(self, a, w, out, act, order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles, max_tiles, places=0):
+    def moe_gemm(self, a, w, out, act, order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles, max_tiles, tile):
         self._on_gpu(a, w, out, order, tile_expert, tile_p0, tile_n, n_tiles)
-        from . import MOE_TILE
+        MOE_TILE = tile
         self._check(self.lib.hfb_moe_gemm(_p(a), c_int(_dt(a)), _p(w), c_int(_dt(w)), _p(out), c_int(_dt(out)), c_int(act),
                                           c_int(w.shape[1]), c_int(w.shape[2]), _p(order), c_int(src_div), c_int(1 if scatter else 0),
                                           _p(tile_expert), _p(tile_p0), _p(tile_n), _p(n_tiles), c_int(max_tiles), c_int(MOE_TILE),
-                                          c_int(places), self._stream()), "moe_gemm")
+                                          self._stream()), "moe_gemm")
 
     def moe_combine(self, y, weights, out):
         self._on_gpu(y, weights, out)

@@ -173,8 +173,8 @@ class EmuBackend:
         ids.copy_(idx[:, :top].int())
         weights.copy_(torch.softmax(zc[:, :top], -1))
 
-    def moe_group(self, ids, experts, order, tile_expert, tile_p0, tile_n, n_tiles):
-        from hfcpu_b200.kernels import MOE_TILE
+    def moe_group(self, ids, experts, order, tile_expert, tile_p0, tile_n, n_tiles, tile):
+        MOE_TILE = tile
         flat = ids.reshape(-1)
         srt = torch.sort(flat, stable=True).indices.int()
         order[:flat.numel()] = srt
@@ -187,7 +187,7 @@ class EmuBackend:
             at += c
         n_tiles[0] = n
 
-    def moe_gemm(self, a, w, out, act, order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles, max_tiles, places=0):
+    def moe_gemm(self, a, w, out, act, order, src_div, scatter, tile_expert, tile_p0, tile_n, n_tiles, max_tiles, tile):
         assert int(n_tiles[0]) <= max_tiles
         for i in range(int(n_tiles[0])):
             e, p0, n = int(tile_expert[i]), int(tile_p0[i]), int(tile_n[i])
