@@ -253,7 +253,8 @@ def compare_configs(z):
 def phase_work(model, q_len, ctx_len, batch):
     """Per phase of the forward pass: (operations, bytes that must move) of one step of ``batch`` requests that bring
     ``q_len`` tokens each and hold ``ctx_len`` afterwards, summed over the layers: what the roofline of each phase's
-    kernels is made of.  Weights are read once a step; a routed layer reads the experts its tokens choose (at most all)."""
+    kernels is made of.  Weights are read once a step; a routed layer reads the experts its tokens choose: with random
+    weights the choices are close to uniform, so n (1 - (1 - 1/n)^(T top)) of n experts are expected to be chosen."""
     T = batch * q_len
     el = 2
     work = {k: [0.0, 0.0] for k in ("qkv", "attn", "wo", "gate_up", "down", "head")}
@@ -273,7 +274,7 @@ def phase_work(model, q_len, ctx_len, batch):
             add("gate_up", 2.0 * T * f.w_gate_up.numel(), el * (f.w_gate_up.numel() + T * (f.E + f.F)))
             add("down", 2.0 * T * f.w_down.numel(), el * (f.w_down.numel() + T * f.F) + 4 * T * f.E)
         elif f is not None:
-            used = min(f.n, T * f.top)
+            used = f.n * (1.0 - (1.0 - 1.0 / f.n) ** (T * f.top))
             add("gate_up", 2.0 * T * f.E * (f.top * f.F + f.FS), el * (f.E * (used * f.F + f.FS) + T * (f.E + f.top * f.F + f.FS)))
             add("down", 2.0 * T * f.E * (f.top * f.F + f.FS), el * (f.E * (used * f.F + f.FS) + T * (f.top * f.F + f.FS)) + 4 * T * f.E * (f.top + 1))
     return work
@@ -329,7 +330,8 @@ def run_compare(args):
             held = [P]
 
             def decode():
-                eng.step([StepEntry(b, [7], [0]) for b in range(B)])
+                # a different token for every request and step, so that the requests of a step choose different experts
+                eng.step([StepEntry(b, [(7919 * held[0] + 104729 * b) % V], [0]) for b in range(B)])
                 held[0] += 1
             for kind, fn, q_len, batch in (("prefill", prefill, P, 1), ("decode", decode, 1, B)):
                 ms, _ = timed(fn, args.steps if kind == "decode" else 5, False)
