@@ -55,23 +55,32 @@ class SandwichResidual(Block):
         else:
             xn = xn_ready
         y = ctx.buf("block_y", x.shape, torch.float32)
+        # A part whose output is a product may hand that product to the norm behind it (``forward_into_norm``), which
+        # then sums the product's partial sums in its own pass; else the part stores its output in y and the norm adds it.
+        # Either way the norm returns whether the following norm of the new stream came out of the same pass.
+        fused_norms = hasattr(post1, "add_product_into")
 
-        def sublayer(part, post, nn, out, *args):
-            """x += post(part(...)); returns whether ``out = nn(x)`` came out of the same pass.  A part whose output is a
-            product hands that product to the norm (``forward_into_norm``), which may sum its partial sums itself."""
-            into = getattr(part, "forward_into_norm", None) if hasattr(post, "add_product_into") else None
+        def mix(following, out):
+            into = getattr(mixer, "forward_into_norm", None) if fused_norms else None
             if into is not None:
-                return into(ctx, *args, y, x, post, nn, out)
-            part.forward(ctx, *args, y, accumulate=False) if part is ffn else part.forward(ctx, *args[:1], y, *args[1:], accumulate=False)
-            return post.add_into(y, x, nn, out)
-        if ffn is None:
-            nxt = ctx.buf("block_xn", x.shape, ctx.run_dtype) if next_norm is not None else None
-            return nxt if sublayer(mixer, post1, next_norm, nxt, xn, cache, state, write_cache) else None
-        xn2 = ctx.buf("block_xn2", x.shape, ctx.run_dtype)
-        if not sublayer(mixer, post1, norm2, xn2, xn, cache, state, write_cache):
-            norm2.forward(x, xn2)
+                return into(ctx, xn, cache, state, write_cache, y, x, post1, following, out)
+            mixer.forward(ctx, xn, y, cache, state, write_cache, accumulate=False)
+            return post1.add_into(y, x, following, out)
+
+        def feed_forward(xin, following, out):
+            into = getattr(ffn, "forward_into_norm", None) if fused_norms else None
+            if into is not None:
+                return into(ctx, xin, y, x, post2, following, out)
+            ffn.forward(ctx, xin, y, accumulate=False)
+            return post2.add_into(y, x, following, out)
+
         nxt = ctx.buf("block_xn", x.shape, ctx.run_dtype) if next_norm is not None else None
-        return nxt if sublayer(ffn, post2, next_norm, nxt, xn2) else None
+        if ffn is None:
+            return nxt if mix(next_norm, nxt) else None
+        xn2 = ctx.buf("block_xn2", x.shape, ctx.run_dtype)
+        if not mix(norm2, xn2):
+            norm2.forward(x, xn2)
+        return nxt if feed_forward(xn2, next_norm, nxt) else None
 
 
 register_part("block", "prenorm_residual", PreNormResidual)
