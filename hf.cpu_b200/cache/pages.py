@@ -97,7 +97,12 @@ class CacheGroup:
         self.block_size, self.num_pages = block_size, num_pages
         self.pool = PagePool(num_pages)
         shape = (len(self.entries), num_pages, block_size, spec.num_kv_heads)
-        if spec.value_dim == spec.head_dim:
+        if spec.values_in_keys:
+            # one array of rows; whoever reads values reads them out of the keys
+            self.storage = None
+            self.keys = torch.zeros(shape + (spec.head_dim,), dtype=dtype, device=device)
+            self.values = None
+        elif spec.value_dim == spec.head_dim:
             # keys and values of an entry side by side in one array (a kernel may fetch both through one map)
             self.storage = torch.zeros((shape[0], 2) + shape[1:] + (spec.head_dim,), dtype=dtype, device=device)
             self.keys, self.values = self.storage[:, 0], self.storage[:, 1]
@@ -115,13 +120,11 @@ class CacheGroup:
 
     def layer_cache(self, entry: int) -> LayerCache:
         i = self.entries.index(entry)
-        return LayerCache(self.index, self.keys[i], self.values[i])
+        return LayerCache(self.index, self.keys[i], self.values[i] if self.values is not None else None)
 
     def first_needed_block(self, next_pos: int) -> int:
         """Blocks before this one hold no key that a query at ``next_pos`` or later can see."""
-        if self.spec.window <= 0:
-            return 0
-        return max(0, next_pos - self.spec.window + 1) // self.block_size
+        return self.spec.first_visible(next_pos) // self.block_size
 
     def blocks_to_map(self, table: List[int], old_len: int, new_len: int) -> List[int]:
         """Block indices that must be mapped so positions ``old_len .. new_len-1`` can be written

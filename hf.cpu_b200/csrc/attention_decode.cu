@@ -69,8 +69,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int r = p.H / p.G;
     const int seq = p.tile_seq[tile], t0 = p.tile_t0[tile], nt = p.tile_nt[tile];
     const int pos_first = p.positions[t0], pos_last = p.positions[t0 + nt - 1];
-    const int lo_first = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
-    const int lo_last = p.window > 0 ? max(0, pos_last - p.window + 1) : 0;
+    const int lo_first = mask_lo(pos_first, p.window);
+    const int lo_last = mask_lo(pos_last, p.window);
     int kt_lo = lo_first / ABN, kt_hi = pos_last / ABN + 1;
     if (p.splits > 1) {
         int per = (kt_hi - kt_lo + p.splits - 1) / p.splits;
@@ -146,7 +146,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         const int tl0 = row0 / r, tl1 = row1 / r;
         const bool v0 = tl0 < nt, v1 = tl1 < nt;
         const int pos0 = v0 ? p.positions[t0 + tl0] : -1, pos1 = v1 ? p.positions[t0 + tl1] : -1;
-        const int lo0 = p.window > 0 ? max(0, pos0 - p.window + 1) : 0, lo1 = p.window > 0 ? max(0, pos1 - p.window + 1) : 0;
+        const int lo0 = mask_lo(pos0, p.window), lo1 = mask_lo(pos1, p.window);
         const int kbase = warp * 16, mi = lane >> 3;
         // the 8 keys whose rows this lane names to ldmatrix lie in one page (pages hold 8 keys or more)
         const int bs = p.block_size;

@@ -35,7 +35,7 @@ attention_fast_kernel(AttnParams p, int *err)
     const int seq = p.tile_seq[tile], t0 = p.tile_t0[tile], nt = p.tile_nt[tile];
     const int32_t *table = p.block_table + (size_t)seq * p.max_blocks;
     const int pos_first = p.positions[t0], pos_last = p.positions[t0 + nt - 1];
-    const int lo_all = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int lo_all = mask_lo(pos_first, p.window);
     int kt_lo = lo_all / ABN, kt_hi = pos_last / ABN + 1;                 // key tiles [kt_lo, kt_hi)
     if (p.splits > 1) {
         int per = (kt_hi - kt_lo + p.splits - 1) / p.splits;
@@ -79,7 +79,7 @@ attention_fast_kernel(AttnParams p, int *err)
     const int tl0 = row0 / r, tl1 = row1 / r;
     const bool v0 = tl0 < nt, v1 = tl1 < nt;
     const int pos0 = v0 ? p.positions[t0 + tl0] : -1, pos1 = v1 ? p.positions[t0 + tl1] : -1;
-    const int lo0 = p.window > 0 ? max(0, pos0 - p.window + 1) : 0, lo1 = p.window > 0 ? max(0, pos1 - p.window + 1) : 0;
+    const int lo0 = mask_lo(pos0, p.window), lo1 = mask_lo(pos1, p.window);
 
     const bool warp_active = warp * 16 < nt * r;      // a warp whose 16 rows are all padding only helps with the loads
     float o[D / 8][4];
@@ -121,7 +121,7 @@ attention_fast_kernel(AttnParams p, int *err)
         // tile's first position and inside every window) needs no per-element test.
         float mx0 = -INFINITY, mx1 = -INFINITY;
         const bool all_visible = v0 && v1 && kt * ABN + ABN - 1 <= pos_first &&
-                                 (p.window == 0 || kt * ABN >= max(0, pos_last - p.window + 1));
+                                 kt * ABN >= mask_lo(pos_last, p.window);
         if (all_visible) {
 #pragma unroll
             for (int i = 0; i < ABN / 8; i++) {

@@ -5,7 +5,9 @@
 // (src/model.c:499-528, src/mathx.c:77-86).  Each warp takes every fourth key with a running
 // maximum and sum; the four partial results are merged in a fixed order, so the result depends
 // only on (lo, pos) and the values, never on what else is in the batch.  Value heads may have another size (dv)
-// than query/key heads (d): the output row of a head has dv elements.
+// than query/key heads (d): the output row of a head has dv elements.  Consecutive value rows lie v_row elements apart:
+// dv for an array of values, d when the values are the first dv elements of the keys themselves (one latent row per
+// token that serves as key and, without its last elements, as value).
 #include "common.cuh"
 
 static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
@@ -14,25 +16,25 @@ namespace hfb {
 int *error_word();
 
 constexpr int ATT_WARPS = 4;
-constexpr int MAX_D_PER_LANE = 8;      // head_dim <= 256
+constexpr int MAX_D_PER_LANE = 20;     // head sizes up to 640
 
-template <typename T>
+template <typename T, int MAX_D_PER_LANE>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_plain_kernel(const T *q, const T *k_cache, const T *v_cache, const int32_t *block_table, int max_blocks,
                        const int32_t *token_seq, const int32_t *positions, int block_size, long long num_pages,
-                       int window, float scale, T *out, int H, int G, int d, int dv, int *err)
+                       int window, float scale, T *out, int H, int G, int d, int dv, int v_row, int *err)
 {
     pdl_sync();
     int t = blockIdx.x, h = blockIdx.y;
     int g = h / (H / G);
     int seq = token_seq[t], pos = positions[t];
-    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    int lo = mask_lo(pos, window);
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int32_t *table = block_table + (size_t)seq * max_blocks;
 
-    __shared__ float sq[256];
+    __shared__ float sq[32 * MAX_D_PER_LANE];
     __shared__ float s_m[ATT_WARPS], s_l[ATT_WARPS];
-    __shared__ float s_acc[ATT_WARPS][256];
+    __shared__ float s_acc[ATT_WARPS][32 * MAX_D_PER_LANE];
     const T *qr = q + ((size_t)t * H + h) * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) sq[i] = to_f32(qr[i]);
     __syncthreads();
@@ -46,7 +48,7 @@ attention_plain_kernel(const T *q, const T *k_cache, const T *v_cache, const int
         long long page = blk < max_blocks ? table[blk] : -1;
         if (page < 0 || page >= num_pages) { if (lane == 0) atomicOr(err, HFB_ERR_PAGE); continue; }
         const size_t at = ((size_t)page * block_size + (j % block_size)) * G + g;
-        const size_t base = at * d, vbase = at * dv;
+        const size_t base = at * d, vbase = at * v_row;
         float dot = 0.f;
 #pragma unroll
         for (int i = 0; i < MAX_D_PER_LANE; i++) {
@@ -96,22 +98,21 @@ using namespace hfb;
 extern "C" int hfb_attention_plain(const void *q, const void *k_cache, const void *v_cache, int dt,
                                    const int32_t *block_table, int max_blocks, const int32_t *token_seq,
                                    const int32_t *positions, int block_size, int64_t num_pages, int window,
-                                   float scale, void *out, int T, int H, int G, int d, int dv, hfb_stream s)
+                                   float scale, void *out, int T, int H, int G, int d, int dv, int v_row, hfb_stream s)
 {
     if (T <= 0) return HFB_OK;
-    if (!valid_dt(dt) || H <= 0 || G <= 0 || H % G || block_size <= 0 || max_blocks <= 0 || window < 0)
+    if (!valid_dt(dt) || H <= 0 || G <= 0 || H % G || block_size <= 0 || max_blocks <= 0 || v_row < dv)
         return fail(HFB_EINVAL, "attention: bad arguments (H=%d G=%d block=%d)", H, G, block_size);
     if (d <= 0 || d > 32 * MAX_D_PER_LANE || dv <= 0 || dv > 32 * MAX_D_PER_LANE)
         return fail(HFB_ENOTSUP, "attention: head sizes %d / %d are not supported (1..%d)", d, dv, 32 * MAX_D_PER_LANE);
     if (H > 65535) return fail(HFB_ENOTSUP, "attention: %d heads exceed the grid limit", H);
     dim3 grid(T, H);
-    if (dt == HFB_F32)
-        g_launch_err = launch_pdl(attention_plain_kernel<float>, dim3(grid), dim3(ATT_WARPS * 32), 0, (cudaStream_t)s, (const float *)q, (const float *)k_cache,
-            (const float *)v_cache, block_table, max_blocks, token_seq, positions, block_size, num_pages, window, scale,
-            (float *)out, H, G, d, dv, error_word());
-    else
-        g_launch_err = launch_pdl(attention_plain_kernel<__nv_bfloat16>, dim3(grid), dim3(ATT_WARPS * 32), 0, (cudaStream_t)s, (const __nv_bfloat16 *)q,
-            (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, block_table, max_blocks, token_seq, positions,
-            block_size, num_pages, window, scale, (__nv_bfloat16 *)out, H, G, d, dv, error_word());
+    const bool small = d <= 256 && dv <= 256;
+#define HFB_PLAIN_ATT(TY, L) \
+    g_launch_err = launch_pdl(attention_plain_kernel<TY, L>, dim3(grid), dim3(ATT_WARPS * 32), 0, (cudaStream_t)s, (const TY *)q, (const TY *)k_cache, \
+        (const TY *)v_cache, block_table, max_blocks, token_seq, positions, block_size, num_pages, window, scale, (TY *)out, H, G, d, dv, v_row, error_word())
+    if (dt == HFB_F32) { if (small) HFB_PLAIN_ATT(float, 8); else HFB_PLAIN_ATT(float, MAX_D_PER_LANE); }
+    else { if (small) HFB_PLAIN_ATT(__nv_bfloat16, 8); else HFB_PLAIN_ATT(__nv_bfloat16, MAX_D_PER_LANE); }
+#undef HFB_PLAIN_ATT
     return check_pdl_launch(g_launch_err, "attention_plain");
 }

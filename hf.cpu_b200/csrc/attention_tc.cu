@@ -94,7 +94,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     const int r = p.H / p.G;
     const int seq = p.tile_seq[tile], t0 = p.tile_t0[tile], nt = p.tile_nt[tile];
     const int pos_first = p.positions[t0], pos_last = p.positions[t0 + nt - 1];
-    const int lo_all = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int lo_all = mask_lo(pos_first, p.window);
     const int kt_lo = lo_all / TKEYS, n_kt = pos_last / TKEYS + 1 - kt_lo;
 
     if (warp == 0) {
@@ -185,7 +185,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             if (lane == 0) mbar_arrive(q_ready);
         }
         const int pos = valid ? p.positions[t0 + tl] : -1;
-        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const int lo = mask_lo(pos, p.window);
         const uint32_t tS = tmem_base + ((uint32_t)(q4 * 32) << 16) + half * 64, tPV = tmem_base + ((uint32_t)(q4 * 32) << 16) + 128 + half * 64;
         float o[64];
 #pragma unroll

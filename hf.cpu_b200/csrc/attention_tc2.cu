@@ -125,7 +125,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
         it.nt0 = min(nt, p.per); it.nt1 = nt - it.nt0;                  // tokens of the two query tiles
         const int pos_first = p.positions[it.t0], pos_last0 = p.positions[it.t0 + it.nt0 - 1];
         it.pos_last = p.positions[it.t0 + nt - 1];
-        const int lo_all = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+        const int lo_all = mask_lo(pos_first, p.window);
         it.kt_lo = lo_all / U_KEYS;
         it.n_kt0 = pos_last0 / U_KEYS + 1 - it.kt_lo;
         it.n_kt1 = it.nt1 > 0 ? it.pos_last / U_KEYS + 1 - it.kt_lo : 0;
@@ -279,7 +279,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                 if (lane == 0) mbar_arrive(q_ready + 8 * i);
             }
             const int pos = valid ? p.positions[t_first + tl] : -1;
-            const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+            const int lo = mask_lo(pos, p.window);
             float m_ref = -INFINITY, l = 0.f;        // the maximum the exponentials refer to, and the sum in its scale
             for (int j = 0; j < n_mine && ok; j++) {
                 const uint32_t ph = (g_mine + j) & 1;

@@ -140,6 +140,16 @@ __device__ __forceinline__ void rope_pair(float a, float b, float c, float s, fl
     hi = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
 }
 
+// The first key a query at `pos` sees, from the one number that names a layer's mask: window > 0, itself and the
+// window - 1 positions before it; window < 0, the keys of its own chunk of -window positions, chunks counted from
+// position 0 of the request; 0, every key.  Never decreases as pos grows, which the tiled kernels rely on.
+__device__ __forceinline__ int mask_lo(int pos, int window)
+{
+    if (window > 0) return max(0, pos - window + 1);
+    if (window < 0) return pos < 0 ? 0 : pos / (-window) * (-window);
+    return 0;
+}
+
 // Index of the current device (0 where it cannot be told), for what is remembered per device.
 inline int current_device()
 {

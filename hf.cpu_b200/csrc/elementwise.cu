@@ -36,6 +36,56 @@ __global__ void embed_kernel(const int32_t *ids, const void *table, int dt, floa
     for (int i = threadIdx.x; i < E; i += blockDim.x) out[(size_t)t * E + i] = load_any(table, dt, base + i);
 }
 
+// ---- embedding with a scale and a hashed pair term -------------------------------------------------
+// One block per token.  The token before a request's first token of the step is per-request state (token + 1, 0 = none
+// yet); only the block of that first token touches the request's state: it reads it, and afterwards leaves the request's
+// last token of the step there, so no two blocks meet on one word.
+__global__ void embed_pair_kernel(const int32_t *ids, const void *table, int dt, float scale, const void *pair, int pair_dt,
+                                  int buckets, long long mul_prev, long long mul_cur, const int32_t *token_seq,
+                                  const int32_t *cu_tokens, const int32_t *seq_slots, int32_t *prev_state, int n_slots,
+                                  float *out, int V, int E, int *err)
+{
+    pdl_entry();
+    pdl_sync_small();
+    __shared__ long long s_row;
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool bad = id < 0 || id >= V;
+    if (threadIdx.x == 0) {
+        long long row = -1;
+        if (bad) atomicOr(err, HFB_ERR_TOKEN_ID);
+        if (pair) {
+            const int sq = token_seq[t], first = cu_tokens[sq];
+            int prev;
+            if (t == first) {
+                const int slot = seq_slots[sq];
+                if (slot < 0 || slot >= n_slots) { atomicOr(err, HFB_ERR_SLOT); prev = -1; }
+                else {
+                    prev = prev_state[slot] - 1;
+                    const int last = ids[cu_tokens[sq + 1] - 1];
+                    prev_state[slot] = (last < 0 || last >= V) ? 0 : last + 1;
+                }
+            } else prev = ids[t - 1];
+            if (prev >= V) { atomicOr(err, HFB_ERR_TOKEN_ID); prev = -1; }
+            if (!bad) row = prev < 0 ? (long long)buckets : ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+        }
+        s_row = row;
+    }
+    __syncthreads();
+    const long long row = s_row;
+    float *o = out + (size_t)t * E;
+    if (bad) {
+        for (int i = threadIdx.x; i < E; i += blockDim.x) o[i] = 0.f;
+        return;
+    }
+    const size_t base = (size_t)id * E, pbase = (size_t)(row < 0 ? 0 : row) * E;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+        float v = load_any(table, dt, base + i) * scale;
+        if (row >= 0) v += load_any(pair, pair_dt, pbase + i);
+        o[i] = v;
+    }
+}
+
 // ---- RMSNorm (src/mathx.c:65-75): products and sum in float32 ---------------------------------
 __global__ void rmsnorm_kernel(const float *x, const void *w, int w_dt, float eps, void *out, int out_dt,
                                const int32_t *rows, int E)
@@ -292,6 +342,22 @@ extern "C" int hfb_embed(const int32_t *ids, const void *table, int table_dt, fl
     if (!valid_dt(table_dt) || V <= 0 || E <= 0) return fail(HFB_EINVAL, "embed: bad arguments");
     g_launch_err = launch_pdl(embed_kernel, dim3(T), dim3(256), 0, (cudaStream_t)s, ids, table, table_dt, out, V, E, error_word());
     return check_pdl_launch(g_launch_err, "embed");
+}
+
+extern "C" int hfb_embed_pair(const int32_t *ids, const void *table, int table_dt, float scale, const void *pair, int pair_dt,
+                              int buckets, int64_t mul_prev, int64_t mul_cur, const int32_t *token_seq,
+                              const int32_t *cu_tokens, const int32_t *seq_slots, int32_t *prev_state, int n_slots,
+                              float *out, int T, int V, int E, hfb_stream s)
+{
+    if (T <= 0) return HFB_OK;
+    if (!valid_dt(table_dt) || V <= 0 || E <= 0) return fail(HFB_EINVAL, "embed_pair: bad arguments");
+    if (pair && (!valid_dt(pair_dt) || buckets <= 0 || mul_prev < 0 || mul_cur < 0 || !token_seq || !cu_tokens || !seq_slots ||
+                 !prev_state || n_slots <= 0))
+        return fail(HFB_EINVAL, "embed_pair: the pair term needs its table, multipliers, the step's arrays and the state");
+    g_launch_err = launch_pdl(embed_pair_kernel, dim3(T), dim3(128), 0, (cudaStream_t)s, ids, table, table_dt, scale, pair, pair_dt, buckets,
+                              (long long)mul_prev, (long long)mul_cur, token_seq, cu_tokens, seq_slots, prev_state, n_slots, out, V, E,
+                              error_word());
+    return check_pdl_launch(g_launch_err, "embed_pair");
 }
 
 extern "C" int hfb_rmsnorm(const float *x, const void *w, int w_dt, float eps, void *out, int out_dt,

@@ -29,6 +29,17 @@ int hfb_version(void);
 /* x[t, :] = table[ids[t], :] as float32.  ids outside [0, V) raise the device error word. */
 int hfb_embed(const int32_t *ids, const void *table, int table_dt, float *out, int T, int V, int E, hfb_stream s);
 
+/* x[t, :] = table[ids[t], :] * scale + pair[row(t), :] as float32, where row(t) hashes the token with the one before it
+ * in its request: (previous * mul_prev + ids[t] * mul_cur) mod buckets, and row `buckets` (the table's last) for a
+ * request's first token.  The previous token of a request's first token in this step comes from prev_state[slot of the
+ * request] (token + 1; 0 = the request has no token yet), which the kernel then sets to the request's last token of
+ * the step.  token_seq [T], cu_tokens [S + 1], seq_slots [S] as the step function builds them.  pair == NULL: no pair
+ * term and no state. */
+int hfb_embed_pair(const int32_t *ids, const void *table, int table_dt, float scale, const void *pair, int pair_dt,
+                   int buckets, int64_t mul_prev, int64_t mul_cur, const int32_t *token_seq, const int32_t *cu_tokens,
+                   const int32_t *seq_slots, int32_t *prev_state, int n_slots, float *out, int T, int V, int E,
+                   hfb_stream s);
+
 /* out[m, :] = x[rows ? rows[m] : m, :] * rsqrt(mean(x^2) + eps) * w, sums in float32. */
 int hfb_rmsnorm(const float *x, const void *w, int w_dt, float eps, void *out, int out_dt,
                 const int32_t *rows, int M, int E, hfb_stream s);
@@ -93,13 +104,16 @@ int hfb_rope_kv_write(const void *qkv, int dt, const float *cos_sin, int n_rot, 
                       const int32_t *positions, const int32_t *slots, void *q_out, void *k_cache, void *v_cache,
                       int64_t cache_slots, int T, int H, int G, int d, hfb_stream s);
 
-/* Attention of every token over its request's cached keys lo..pos (lo = max(0, pos - window + 1) when
- * window > 0, else 0), plain kernel: one block per (token, head), float32 softmax.  Keys [.., G, d], values
- * [.., G, dv], out [T, H dv]. */
+/* Attention of every token over its request's cached keys lo..pos, plain kernel: one block per (token, head), float32
+ * softmax.  `window` names the mask, here and in every attention entry point below: > 0, lo = max(0, pos - window + 1)
+ * (a sliding window); < 0, lo = pos - pos % (-window) (chunks of -window positions counted from position 0: a query
+ * sees the keys of its own chunk); 0, lo = 0.  Keys [.., G, d], values [.., G, dv] with rows v_row elements apart
+ * (dv; or d with v_cache == k_cache, when a value is the first dv elements of its key), out [T, H dv].  Head sizes up
+ * to 640. */
 int hfb_attention_plain(const void *q, const void *k_cache, const void *v_cache, int dt,
                         const int32_t *block_table, int max_blocks, const int32_t *token_seq,
                         const int32_t *positions, int block_size, int64_t num_pages, int window, float scale,
-                        void *out, int T, int H, int G, int d, int dv, hfb_stream s);
+                        void *out, int T, int H, int G, int d, int dv, int v_row, hfb_stream s);
 
 /* The same for bfloat16 with head_dim 64 or 128 and a block size that divides 64, tiled, on tensor cores.
  * Tiles (tile_seq, tile_t0 = first token index, tile_nt = tokens) cover the step's tokens; a tile holds at
@@ -169,12 +183,37 @@ int hfb_dyt_residual(const void *y, int y_dt, int splits, const void *bias, int 
                      void *out, int out_dt, int M, int E, hfb_stream s);
 
 /* The tail of a q|k|v product: src [splits, T, H d + G d + G dv] float32 partial sums (+ bias) -> rotation of the first
- * n_rot dimensions of query and key heads -> with norm != 0, x / sqrt(mean(x^2) + eps) per head -> q_out [T, H d], keys
- * [.., G, d] and values [.., G, dv] at cache slot slots[t].  G == 0: the row holds queries only. */
+ * n_rot dimensions of query and key heads -> with norm != 0, x / sqrt(mean(x^2) + eps) per head, times q_w / k_w
+ * (float32 [d], shared by the heads; null: no weight) -> q_out [T, H d], keys [.., G, d] and values [.., G, dv] at cache
+ * slot slots[t].  G == 0: the row holds queries only.  Values mixed across layers: v_mode 1 copies the row's values to
+ * v_first [T, G dv] (float32) as they are; v_mode 2 replaces them by (1 - v_lambda) v + v_lambda v_first before they
+ * are stored; 0: neither. */
 int hfb_rope_norm_kv_write(const float *src, int splits, const void *bias, int bias_dt, const float *cos_sin,
                            int n_rot, int n_positions, const int32_t *positions, const int32_t *slots,
                            void *q_out, void *k_cache, void *v_cache, int out_dt, int64_t cache_slots, int T,
-                           int H, int G, int d, int dv, int norm, float eps, hfb_stream s);
+                           int H, int G, int d, int dv, int norm, float eps, const float *q_w, const float *k_w,
+                           float *v_first, int v_mode, float v_lambda, hfb_stream s);
+
+/* Latent attention, the tail of the down product: src [splits, T, q_rank + kv_rank + rot] float32 partial sums ->
+ * query latent = rmsnorm(src[:q_rank]) * q_w -> cq_out [T, q_rank]; key/value latent = rmsnorm(next kv_rank) * kv_w ->
+ * cache row [0, kv_rank); the last `rot` values rotated (pairs (2i, 2i+1), cos_sin [n_positions, rot / 2, 2]) -> cache
+ * row [kv_rank, kv_rank + rot).  The cache holds one row of kv_rank + rot per slot.  Norm weights float32. */
+int hfb_latent_split(const float *src, int splits, const float *q_w, const float *kv_w, float eps, const float *cos_sin,
+                     int n_positions, const int32_t *positions, const int32_t *slots, void *cq_out, void *cache,
+                     int out_dt, int64_t cache_slots, int T, int q_rank, int kv_rank, int rot, hfb_stream s);
+
+/* Latent attention, the tail of the query product: src [splits, T, H (d + rot)] float32 partial sums; per head the
+ * first d values go to q_plain [T, H, d] as they are, the last `rot` rotated (pairs (2i, 2i+1)) to
+ * q_att [T, H, att_row] at column att_col. */
+int hfb_latent_query_rope(const float *src, int splits, const float *cos_sin, int n_positions, const int32_t *positions,
+                          void *q_plain, void *q_att, int out_dt, int T, int H, int d, int rot, int att_row, int att_col,
+                          hfb_stream s);
+
+/* A product per head: out[t, h, n] = sum_k w[h, n, k] * in[t, h, k], n < N, k < K; rows of `in` hold H heads in_row
+ * apart from column 0, rows of `out` H heads out_row apart (in_row >= K, out_row >= N: a head's result may land in the
+ * first N columns of a wider row).  float32 sums, any mix of element types. */
+int hfb_headwise_linear(const void *in, int in_dt, const void *w, int w_dt, void *out, int out_dt, int T, int H, int N,
+                        int K, int in_row, int out_row, hfb_stream s);
 
 /* The choice of a mixture of experts' router from its float32 logits z [splits, T, E] (partial sums of the router's
  * product, summed in order, plus its bias; finished logits: splits = 1, bias null): the `top` largest (lowest index first

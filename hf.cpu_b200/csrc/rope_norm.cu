@@ -2,7 +2,11 @@
 // after the rotation, whose value heads may have another size than the key heads, and whose layer may have no
 // keys and values of its own (it reads another layer's cache): sum of split-K partials + bias -> rotation of the
 // first n_rot dimensions (pairs i, i + n_rot/2) -> x / sqrt(mean(x^2) + eps) over the head -> queries to q_out,
-// keys and values to the token's cache slot.  Everything between the float32 sums and the stores is float32.
+// times a weight shared by the heads where the layer has one -> queries to q_out, keys and values to the token's cache
+// slot.  A layer whose values are mixed with those of an earlier layer (v <- (1 - lambda) v + lambda v_first, v_first the
+// same token's values in the first such layer) does that here, before the store, so that the cache holds the mixed
+// values; the first such layer leaves its own values behind for the others.  Everything between the float32 sums and the
+// stores is float32.
 #include "common.cuh"
 
 static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
@@ -18,7 +22,8 @@ template <typename TO>
 __global__ void __launch_bounds__(RN_WARPS * 32)
 rope_norm_kv_kernel(const float *src, int splits, const void *bias, int bias_dt, const float *cos_sin, int n_rot,
                     int n_positions, const int32_t *positions, const int32_t *slots, TO *q_out, TO *k_cache, TO *v_cache,
-                    long long cache_slots, int T, int H, int G, int d, int dv, int norm, float eps, int *err)
+                    long long cache_slots, int T, int H, int G, int d, int dv, int norm, float eps, const float *q_w,
+                    const float *k_w, float *v_first, int v_mode, float v_lambda, int *err)
 {
     pdl_entry();
     pdl_sync_small();
@@ -52,9 +57,16 @@ rope_norm_kv_kernel(const float *src, int splits, const void *bias, int bias_dt,
     }
     __syncwarp();
     if (is_value) {
-        for (int c = lane; c < n; c += 32) dst[c] = from_f32<TO>(x[c]);
+        float *first = v_first ? v_first + (size_t)t * G * dv + (size_t)(u - H - G) * dv : nullptr;
+        for (int c = lane; c < n; c += 32) {
+            float v = x[c];
+            if (v_mode == 1) first[c] = v;
+            else if (v_mode == 2) v = (1.0f - v_lambda) * v + v_lambda * first[c];
+            dst[c] = from_f32<TO>(v);
+        }
         return;
     }
+    const float *w = u < H ? q_w : k_w;
     const int half = n_rot / 2;
     if (half > 0) {
         int pos = positions[t];
@@ -75,7 +87,8 @@ rope_norm_kv_kernel(const float *src, int splits, const void *bias, int bias_dt,
         ss = warp_sum(ss);
         r = 1.0f / sqrtf(ss / (float)n + eps);
     }
-    for (int c = lane; c < n; c += 32) dst[c] = from_f32<TO>(x[c] * r);
+    if (norm && w) { for (int c = lane; c < n; c += 32) dst[c] = from_f32<TO>(x[c] * r * w[c]); }
+    else { for (int c = lane; c < n; c += 32) dst[c] = from_f32<TO>(x[c] * r); }
 }
 
 }  // namespace hfb
@@ -85,7 +98,8 @@ using namespace hfb;
 extern "C" int hfb_rope_norm_kv_write(const float *src, int splits, const void *bias, int bias_dt, const float *cos_sin,
                                       int n_rot, int n_positions, const int32_t *positions, const int32_t *slots,
                                       void *q_out, void *k_cache, void *v_cache, int out_dt, int64_t cache_slots, int T,
-                                      int H, int G, int d, int dv, int norm, float eps, hfb_stream s)
+                                      int H, int G, int d, int dv, int norm, float eps, const float *q_w, const float *k_w,
+                                      float *v_first, int v_mode, float v_lambda, hfb_stream s)
 {
     if (T <= 0) return HFB_OK;
     if (!valid_dt(out_dt) || (bias && !valid_dt(bias_dt)) || splits < 1 || H <= 0 || G < 0 || d <= 0 || dv <= 0 ||
@@ -93,15 +107,16 @@ extern "C" int hfb_rope_norm_kv_write(const float *src, int splits, const void *
         return fail(HFB_EINVAL, "rope_norm_kv_write: bad arguments (H=%d G=%d d=%d dv=%d n_rot=%d)", H, G, d, dv, n_rot);
     if (d > RN_MAX_D || dv > RN_MAX_D) return fail(HFB_ENOTSUP, "rope_norm_kv_write: head sizes above %d are not supported", RN_MAX_D);
     if (n_rot > 0 && (!cos_sin || !positions)) return fail(HFB_EINVAL, "rope_norm_kv_write: rotation needs a table and positions");
+    if (v_mode < 0 || v_mode > 2 || (v_mode && (!v_first || G <= 0))) return fail(HFB_EINVAL, "rope_norm_kv_write: value mixing needs the first layer's values");
     if (G > 0 && slots && (!k_cache || !v_cache)) return fail(HFB_EINVAL, "rope_norm_kv_write: keys and values need a cache");
     const long long items = (long long)T * (H + 2 * G);
     const unsigned blocks = (unsigned)((items + RN_WARPS - 1) / RN_WARPS);
     if (out_dt == HFB_F32)
         g_launch_err = launch_pdl(rope_norm_kv_kernel<float>, dim3(blocks), dim3(RN_WARPS * 32), 0, (cudaStream_t)s, src, splits, bias, bias_dt, cos_sin, n_rot,
-            n_positions, positions, slots, (float *)q_out, (float *)k_cache, (float *)v_cache, (long long)cache_slots, T, H, G, d, dv, norm, eps, error_word());
+            n_positions, positions, slots, (float *)q_out, (float *)k_cache, (float *)v_cache, (long long)cache_slots, T, H, G, d, dv, norm, eps, q_w, k_w, v_first, v_mode, v_lambda, error_word());
     else
         g_launch_err = launch_pdl(rope_norm_kv_kernel<__nv_bfloat16>, dim3(blocks), dim3(RN_WARPS * 32), 0, (cudaStream_t)s, src, splits, bias, bias_dt, cos_sin, n_rot,
             n_positions, positions, slots, (__nv_bfloat16 *)q_out, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, (long long)cache_slots, T, H, G, d, dv, norm, eps,
-            error_word());
+            q_w, k_w, v_first, v_mode, v_lambda, error_word());
     return check_pdl_launch(g_launch_err, "rope_norm_kv_write");
 }

@@ -41,8 +41,7 @@ def decode_step_bytes(engine, kv_lens: Sequence[int]) -> int:
     total = engine.model.weight_bytes_per_step()
     for g in engine.cache.groups:
         per_token = g.page_bytes // engine.block_size
-        w = g.spec.window
-        total += sum((min(n, w) if w > 0 else n) * per_token for n in kv_lens)
+        total += sum((n - g.spec.first_visible(n - 1)) * per_token for n in kv_lens if n > 0)
     return total
 
 

@@ -17,7 +17,7 @@ import numpy as np
 import torch
 
 from ..cache import KVCacheManager, OutOfPages, StateSlots
-from ..models import Model
+from ..models import EMBEDDING_STATE, Model
 
 
 @dataclass
@@ -154,6 +154,8 @@ class Engine:
                 cache_specs[i] = mixer.cache_spec()
             if mixer.state_spec() is not None:
                 state_specs[i] = mixer.state_spec()
+        if model.embedding.state_spec() is not None:
+            state_specs[EMBEDDING_STATE] = model.embedding.state_spec()
         for i, e in enumerate(plan.schedule):
             if e.cache_of is not None and e.cache_of not in cache_specs:
                 raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_of}, which keeps none")

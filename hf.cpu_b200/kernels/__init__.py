@@ -15,7 +15,8 @@ from ..config.base import UnsupportedError
 
 _backend = None
 
-MAX_HEAD_DIM = 256
+MAX_HEAD_DIM = 256          # heads that go through the q|k|v tails
+MAX_LATENT_ROW = 640        # a latent row [latent | rotated part] the plain attention kernel walks
 ERROR_BITS = {1: "a token id outside the vocabulary", 2: "a block-table entry that names no page",
               4: "a cache slot outside the pool", 8: "a device-side wait that ran out",
               16: "a position outside the rotary table"}
@@ -103,6 +104,19 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
     backend().embed(ids, table, out)
 
 
+def embed_pair(ids, table, scale: float, pair, buckets: int, mul_prev: int, mul_cur: int, ctx, prev_state, out) -> None:
+    """out = table[ids] * scale + pair[row], row = (previous * mul_prev + id * mul_cur) mod buckets, or ``buckets`` for a
+    request's first token; ``prev_state`` (int32 [slots]: token + 1, 0 = none) carries the previous token from step to
+    step and is brought up to date.  ``pair`` None: the scaled embedding alone."""
+    _need(ids.dtype == torch.int32 and ids.dim() == 1, "embed_pair: ids must be int32 [T]")
+    _need(out.dtype == torch.float32 and out.shape == (ids.shape[0], table.shape[1]), "embed_pair: out must be float32 [T, E]")
+    if pair is not None:
+        _need(pair.shape == (buckets + 1, table.shape[1]), "embed_pair: the pair table must be [buckets + 1, E]")
+        _need(prev_state is not None and prev_state.dtype == torch.int32 and prev_state.dim() == 1,
+              "embed_pair: the previous tokens must be int32 [slots]")
+    backend().embed_pair(ids, table, float(scale), pair, int(buckets), int(mul_prev), int(mul_cur), ctx, prev_state, out)
+
+
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
     _need(x.dtype == torch.float32 and x.dim() == 2, "rmsnorm: x must be float32 [N, E]")
     _need(w.shape == (x.shape[1],) and out.shape[1] == x.shape[1], "rmsnorm: width mismatch")
@@ -161,10 +175,26 @@ def attention_step_arrays(q_lens, heads_per_group: int):
     return out
 
 
-def paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tiles=None, dv=None) -> None:
-    """``tiles``: the device arrays of :func:`attention_step_arrays` for this step (without them only the plain
-    kernel runs).  ``dv``: the size of a value head where it is not ``d``; ``out`` is then [T, H * dv]."""
+def mask_code(window: int = 0, chunk: int = 0) -> int:
+    """The one number that names a mask to the attention kernels: ``window`` > 0 (a query sees itself and the window - 1
+    positions before it), -``chunk`` (a query sees the keys of its own chunk of that many positions, counted from
+    position 0), or 0 (every key)."""
+    window, chunk = int(window or 0), int(chunk or 0)
+    _need(window >= 0 and chunk >= 0 and not (window and chunk), "a mask is a window or chunks, not both")
+    return window if window else -chunk
+
+
+def paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tiles=None, dv=None, values_in_keys=False) -> None:
+    """``window``: a :func:`mask_code`.  ``tiles``: the device arrays of :func:`attention_step_arrays` for this step
+    (without them only the plain kernel runs).  ``dv``: the size of a value head where it is not ``d``; ``out`` is then
+    [T, H * dv].  ``values_in_keys``: there is no array of values, a value is the first ``dv`` elements of its key."""
     dv = d if dv is None else int(dv)
+    if values_in_keys:
+        _need(0 < dv <= d <= MAX_LATENT_ROW and v_cache is None, "attention: values inside keys need dv <= d <= %d" % MAX_LATENT_ROW)
+        _need(q.shape[1] == H * d and out.shape == (q.shape[0], H * dv) and k_cache.shape[2:] == (G, d), "attention: shape mismatch")
+        _need(q.dtype == k_cache.dtype == out.dtype, "attention: element types differ")
+        backend().paged_attention(q, k_cache, None, meta, ctx, H, G, d, int(window), float(scale), out, tiles or {}, dv=dv)
+        return
     _need(0 < d <= MAX_HEAD_DIM and 0 < dv <= MAX_HEAD_DIM, "attention: head sizes must be 1..%d" % MAX_HEAD_DIM)
     _need(q.shape[1] == H * d and out.shape == (q.shape[0], H * dv), "attention: shape mismatch")
     _need(k_cache.shape[2:] == (G, d) and v_cache.shape[2:] == (G, dv), "attention: cache geometry mismatch")
@@ -283,11 +313,20 @@ def linear_dyt_residual(a, w, bias, y_buf, post, residual, nxt=None, out=None, m
 
 
 def linear_rope_norm_kv(a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d, dv,
-                        norm_eps) -> None:
+                        norm_eps, norm_weights=None, value_mix=None) -> None:
     """The q|k|v product and its tail for attention with unit-rms queries and keys: row = [H heads of d | G key heads
     of d | G value heads of dv] (G = 0: the layer has no keys and values of its own); rotation of the first ``n_rot``
-    dimensions of query and key heads, then, unless ``norm_eps`` is None, x / sqrt(mean(x^2) + eps) per head; queries
-    to ``q_out``, keys and values to the cache at ``slots``.  ``qkv_buf`` [T, row] float32 is scratch."""
+    dimensions of query and key heads, then, unless ``norm_eps`` is None, x / sqrt(mean(x^2) + eps) per head, times
+    ``norm_weights`` = (q weight, k weight), float32 [d] each, where the norm has weights; queries to ``q_out``, keys
+    and values to the cache at ``slots``.  ``value_mix`` = (first [T, G * dv] float32, mode, lambda): mode 1 leaves the
+    row's values in ``first``, mode 2 stores (1 - lambda) v + lambda first instead of v.  ``qkv_buf`` [T, row] float32 is
+    scratch."""
+    if norm_weights is not None:
+        _need(norm_eps is not None and all(x.shape == (d,) and x.dtype == torch.float32 for x in norm_weights),
+              "linear_rope_norm_kv: norm weights are float32 [d] and come with a norm")
+    if value_mix is not None:
+        _need(G > 0 and value_mix[0].shape == (a.shape[0], G * dv) and value_mix[0].dtype == torch.float32 and value_mix[1] in (1, 2),
+              "linear_rope_norm_kv: value mixing takes (float32 [T, G * dv], 1 | 2, lambda)")
     C = H * d + G * (d + dv)
     _need(w.shape[0] == C and q_out.shape == (a.shape[0], H * d) and a.shape[1] == w.shape[1], "linear_rope_norm_kv: shape mismatch")
     _need(qkv_buf.shape == (a.shape[0], C) and qkv_buf.dtype == torch.float32, "linear_rope_norm_kv: scratch must be float32 [T, row]")
@@ -297,8 +336,54 @@ def linear_rope_norm_kv(a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q
               "linear_rope_norm_kv: cache geometry mismatch")
     _need(n_rot == 0 or (cos_sin is not None and cos_sin.shape[1:] == (n_rot // 2, 2) and cos_sin.dtype == torch.float32),
           "linear_rope_norm_kv: cos/sin table must be float32 [positions, n_rot/2, 2]")
+    extra = {}
+    if norm_weights is not None:
+        extra["norm_weights"] = norm_weights
+    if value_mix is not None:
+        extra["value_mix"] = (value_mix[0], int(value_mix[1]), float(value_mix[2]))
     backend().linear_rope_norm_kv(a, w, bias, qkv_buf, cos_sin, int(n_rot), positions, slots, q_out, k_cache, v_cache,
-                                  H, G, d, dv, None if norm_eps is None else float(norm_eps))
+                                  H, G, d, dv, None if norm_eps is None else float(norm_eps), **extra)
+
+
+def linear_latent_split(a, w, buf, q_norm_w, kv_norm_w, eps, cos_sin, positions, slots, cq_out, cache, q_rank, kv_rank, rot) -> None:
+    """Latent attention's down product and its tail: row = a @ w.T = [q_rank | kv_rank | rot]; the first two parts are
+    normed (x / sqrt(mean(x^2) + eps) times a float32 weight), the query latent goes to ``cq_out``, the key/value latent
+    and the last part, rotated in pairs (2i, 2i + 1), form the token's row of ``cache`` [pages, block, 1, kv_rank + rot].
+    ``buf`` [T, row] float32 is scratch."""
+    C = q_rank + kv_rank + rot
+    _need(w.shape[0] == C and a.shape[1] == w.shape[1] and buf.shape == (a.shape[0], C) and buf.dtype == torch.float32,
+          "linear_latent_split: shape mismatch")
+    _need(q_norm_w.shape == (q_rank,) and kv_norm_w.shape == (kv_rank,) and q_norm_w.dtype == kv_norm_w.dtype == torch.float32,
+          "linear_latent_split: norm weights are float32 [q_rank] and [kv_rank]")
+    _need(cq_out.shape == (a.shape[0], q_rank) and cache.shape[2:] == (1, kv_rank + rot) and cache.dtype == cq_out.dtype,
+          "linear_latent_split: output geometry mismatch")
+    _need(rot % 2 == 0 and (rot == 0 or (cos_sin is not None and cos_sin.shape[1:] == (rot // 2, 2) and cos_sin.dtype == torch.float32)),
+          "linear_latent_split: cos/sin table must be float32 [positions, rot/2, 2]")
+    backend().linear_latent_split(a, w, buf, q_norm_w, kv_norm_w, float(eps), cos_sin, positions, slots, cq_out, cache,
+                                  int(q_rank), int(kv_rank), int(rot))
+
+
+def linear_latent_query(a, w, buf, cos_sin, positions, q_plain, q_att, H, d, rot, att_col) -> None:
+    """Latent attention's query product and its tail: row = a @ w.T = H heads of [d plain | rot rotated]; the plain parts
+    go to ``q_plain`` [T, H * d], the rotated ones (pairs (2i, 2i + 1)) into ``q_att`` [T, H * row] at column ``att_col``
+    of each head's row.  ``buf`` [T, H * (d + rot)] float32 is scratch."""
+    T = a.shape[0]
+    _need(w.shape[0] == H * (d + rot) and a.shape[1] == w.shape[1] and buf.shape == (T, w.shape[0]) and buf.dtype == torch.float32,
+          "linear_latent_query: shape mismatch")
+    _need(q_plain.shape == (T, H * d) and q_att.shape[0] == T and q_att.shape[1] % H == 0 and att_col + rot <= q_att.shape[1] // H
+          and q_plain.dtype == q_att.dtype, "linear_latent_query: output geometry mismatch")
+    _need(rot % 2 == 0 and (rot == 0 or (cos_sin is not None and cos_sin.shape[1:] == (rot // 2, 2) and cos_sin.dtype == torch.float32)),
+          "linear_latent_query: cos/sin table must be float32 [positions, rot/2, 2]")
+    backend().linear_latent_query(a, w, buf, cos_sin, positions, q_plain, q_att, int(H), int(d), int(rot), int(att_col))
+
+
+def headwise_linear(x, w, out, H: int, in_row: int, out_row: int) -> None:
+    """A product per head: out[t, h, :N] = w[h] @ x[t, h, :K] with w [H, N, K]; a row of ``x`` holds H heads ``in_row``
+    apart, a row of ``out`` H heads ``out_row`` apart (a head's result may be the first N columns of a wider row)."""
+    _need(w.dim() == 3 and w.shape[0] == H and x.shape[1] == H * in_row and out.shape == (x.shape[0], H * out_row)
+          and in_row >= w.shape[2] and out_row >= w.shape[1], "headwise_linear: shape mismatch")
+    _need(x.dtype == out.dtype == w.dtype, "headwise_linear: element types differ")
+    backend().headwise_linear(x, w, out, int(H), int(in_row), int(out_row))
 
 
 def linear_glu(a: torch.Tensor, w: torch.Tensor, gu_buf: torch.Tensor, out: torch.Tensor, act: str) -> None:

@@ -101,6 +101,16 @@ class NativeBackend:
         self._check(self.lib.hfb_embed(_p(ids), _p(table), c_int(_dt(table)), _p(out), c_int(T), c_int(V), c_int(E),
                                        self._stream()), "embed")
 
+    def embed_pair(self, ids, table, scale, pair, buckets, mul_prev, mul_cur, ctx, prev_state, out):
+        self._on_gpu(ids, table, pair, prev_state, out)
+        T, (V, E) = ids.shape[0], table.shape
+        has = pair is not None
+        self._check(self.lib.hfb_embed_pair(
+            _p(ids), _p(table), c_int(_dt(table)), c_float(scale), _p(pair), c_int(_dt(pair) if has else 0), c_int(buckets),
+            c_int64(mul_prev), c_int64(mul_cur), _p(ctx.token_seq if has else None), _p(ctx.cu_tokens if has else None),
+            _p(ctx.seq_slots if has else None), _p(prev_state if has else None), c_int(prev_state.shape[0] if has else 0),
+            _p(out), c_int(T), c_int(V), c_int(E), self._stream()), "embed_pair")
+
     def rmsnorm(self, x, w, eps, out, rows):
         self._on_gpu(x, w, out, rows)
         M, E = out.shape
@@ -144,8 +154,11 @@ class NativeBackend:
         self._on_gpu(q, k_cache, v_cache, meta.block_table, ctx.token_seq, ctx.positions, out)
         T = q.shape[0]
         dv = d if dv is None else dv
+        v_row = dv
+        if v_cache is None:                   # a value is the first dv elements of its key
+            v_cache, v_row = k_cache, d
         if (self.attention == "fast" and tile_arrays and q.dtype == torch.bfloat16 and d in (64, 128) and dv == d
-                and 64 % meta.block_size == 0):
+                and v_row == dv and 64 % meta.block_size == 0):
             decode = ctx.max_q_len == 1
 
             def tiles(ratio, height):
@@ -234,7 +247,7 @@ class NativeBackend:
                                                  c_int(meta.max_blocks), _p(ctx.token_seq), _p(ctx.positions),
                                                  c_int(meta.block_size), c_int64(k_cache.shape[0]), c_int(window),
                                                  c_float(scale), _p(out), c_int(T), c_int(H), c_int(G), c_int(d), c_int(dv),
-                                                 self._stream()), "attention")
+                                                 c_int(v_row), self._stream()), "attention")
 
     def swiglu(self, gu, out, interleaved):
         self._on_gpu(gu, out)
@@ -363,7 +376,7 @@ class NativeBackend:
             self._stream()), "dyt_residual")
 
     def linear_rope_norm_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d, dv,
-                            norm_eps):
+                            norm_eps, norm_weights=None, value_mix=None):
         self._on_gpu(a, w, bias, cos_sin, positions, slots, q_out, k_cache, v_cache)
         T = a.shape[0]
         part = self._partials(a, w) if self._tc_ok(a, w) else None
@@ -373,12 +386,48 @@ class NativeBackend:
         else:
             src, splits = part
         cache_slots = k_cache.shape[0] * k_cache.shape[1] if G else 0
+        q_w, k_w = norm_weights or (None, None)
+        v_first, v_mode, v_lambda = value_mix or (None, 0, 0.0)
+        self._on_gpu(q_w, k_w, v_first)
         self._check(self.lib.hfb_rope_norm_kv_write(
             _p(src), c_int(splits), _p(bias), c_int(_dt(bias) if bias is not None else 0), _p(cos_sin), c_int(n_rot),
             c_int(cos_sin.shape[0] if cos_sin is not None else 0), _p(positions), _p(slots if G else None), _p(q_out),
             _p(k_cache if G else None), _p(v_cache if G else None), c_int(_dt(q_out)), c_int64(cache_slots), c_int(T), c_int(H),
-            c_int(G), c_int(d), c_int(dv), c_int(0 if norm_eps is None else 1), c_float(norm_eps or 0.0), self._stream()),
+            c_int(G), c_int(d), c_int(dv), c_int(0 if norm_eps is None else 1), c_float(norm_eps or 0.0), _p(q_w), _p(k_w),
+            _p(v_first), c_int(v_mode), c_float(v_lambda), self._stream()),
             "rope_norm_kv_write")
+
+    def _product_sums(self, a, w, buf):
+        """float32 sums of a @ w.T for a tail kernel: (partial sums, splits) where the tensor-core product is split over
+        k (the tail then sums the pieces itself), else the finished product in ``buf`` with splits = 1."""
+        part = self._partials(a, w) if self._tc_ok(a, w) else None
+        if part is not None:
+            return part
+        self.linear(a, w, None, buf, False)
+        return buf, 1
+
+    def linear_latent_split(self, a, w, buf, q_norm_w, kv_norm_w, eps, cos_sin, positions, slots, cq_out, cache, q_rank, kv_rank, rot):
+        self._on_gpu(a, w, buf, q_norm_w, kv_norm_w, cos_sin, positions, slots, cq_out, cache)
+        src, splits = self._product_sums(a, w, buf)
+        self._check(self.lib.hfb_latent_split(
+            _p(src), c_int(splits), _p(q_norm_w), _p(kv_norm_w), c_float(eps), _p(cos_sin),
+            c_int(cos_sin.shape[0] if cos_sin is not None else 0), _p(positions), _p(slots), _p(cq_out), _p(cache), c_int(_dt(cq_out)),
+            c_int64(cache.shape[0] * cache.shape[1]), c_int(a.shape[0]), c_int(q_rank), c_int(kv_rank), c_int(rot), self._stream()),
+            "latent_split")
+
+    def linear_latent_query(self, a, w, buf, cos_sin, positions, q_plain, q_att, H, d, rot, att_col):
+        self._on_gpu(a, w, buf, cos_sin, positions, q_plain, q_att)
+        src, splits = self._product_sums(a, w, buf)
+        self._check(self.lib.hfb_latent_query_rope(
+            _p(src), c_int(splits), _p(cos_sin), c_int(cos_sin.shape[0] if cos_sin is not None else 0), _p(positions), _p(q_plain),
+            _p(q_att), c_int(_dt(q_att)), c_int(a.shape[0]), c_int(H), c_int(d), c_int(rot), c_int(q_att.shape[1] // H), c_int(att_col),
+            self._stream()), "latent_query_rope")
+
+    def headwise_linear(self, x, w, out, H, in_row, out_row):
+        self._on_gpu(x, w, out)
+        self._check(self.lib.hfb_headwise_linear(_p(x), c_int(_dt(x)), _p(w), c_int(_dt(w)), _p(out), c_int(_dt(out)), c_int(x.shape[0]),
+                                                 c_int(H), c_int(w.shape[1]), c_int(w.shape[2]), c_int(in_row), c_int(out_row),
+                                                 self._stream()), "headwise_linear")
 
     def linear_glu(self, a, w, gu_buf, out, act):
         self._on_gpu(a, w, gu_buf, out)

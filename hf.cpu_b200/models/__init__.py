@@ -18,6 +18,9 @@ from ..parts import make_part
 from ..weights import RandomSource, TensorSpec, load_tensors
 
 
+EMBEDDING_STATE = "embedding"        # the key of the embedding's per-request state among the schedule entries' states
+
+
 @dataclass
 class Layer:
     block: object
@@ -109,7 +112,7 @@ class Model:
     def forward(self, ctx) -> Optional[torch.Tensor]:
         T = ctx.token_ids.shape[0]
         x = ctx.buf("residual", (T, self.plan.hidden_size), torch.float32)
-        self.embedding.forward(ctx.token_ids, x)
+        self.embedding.forward(ctx.token_ids, x, ctx=ctx, state=ctx.entry_state(EMBEDDING_STATE))
         schedule = self.plan.schedule
         xn = None                                # norm1 of the coming block, when the previous block computed it
         for i, e in enumerate(schedule):

@@ -12,7 +12,13 @@ not ``1/sqrt(head_dim)``), ``v_head_dim`` (value heads of another size than quer
 the rotation every query and key head is divided by its root mean square, ``x / sqrt(mean(x^2) + eps)``, no weight;
 the cache holds the keys in that form), and ``own_kv=False`` (the layer has no key and value projections: its queries
 attend over the cache of the schedule entry it is pointed at, which a layer with the same head counts and rotation
-has filled).
+has filled).  ``qk_norm_weights`` = {"q": suffix, "k": suffix} names one weight vector [head_dim] each, shared by the heads,
+that the normed queries and keys are multiplied by.  ``chunk`` > 0 replaces the causal mask by a chunked one: a query
+sees the earlier keys of its own chunk of that many positions, chunks counted from position 0 of the request.
+``v_mix``: "first" marks the first layer of a model whose values are mixed into later layers' (its own values stay as
+they are, and it leaves them behind for the step's other layers); "later" replaces a layer's values by
+``(1 - lambda) v + lambda v_first`` before they are cached, ``lambda`` being the scalar tensor ``v_mix_tensor`` and
+``v_first`` the same token's values of the "first" layer, whose value heads must have the same count and size.
 """
 from __future__ import annotations
 
@@ -26,125 +32,9 @@ from ..weights.loader import TensorSpec, fused_rows
 from .base import CacheSpec, Mixer, register_part
 
 
-class PagedAttention(Mixer):
-    graph_safe = True
-
-    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
-                 qkv_bias: bool, out_bias: bool, window: int, position, prefix: str,
-                 positions=None, names=None, scale=None, v_head_dim=None, qk_norm_eps=None, own_kv: bool = True,
-                 bias_suffix: str = ".bias", weight_suffix: str = ".weight", **_):
-        self.E, self.H, self.G, self.d = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
-        if self.H % self.G:
-            raise UnsupportedError(f"unsupported attention geometry: {self.H} heads over {self.G} key/value heads")
-        self.dv = int(v_head_dim) if v_head_dim else self.d
-        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
-        self.own_kv = bool(own_kv)
-        # the q|k|v tail that normalises heads also takes the other two options; the reference's layer keeps its own
-        self.general = self.qk_norm_eps is not None or self.dv != self.d or not self.own_kv
-        if self.general:
-            if not (0 < self.d <= kernels.MAX_HEAD_DIM and 0 < self.dv <= kernels.MAX_HEAD_DIM):
-                raise UnsupportedError(f"head sizes {self.d} / {self.dv} are not supported (1 to {kernels.MAX_HEAD_DIM})")
-        else:
-            kernels.check_head_dim(self.d)
-        self.wsuf, self.bsuf = weight_suffix, bias_suffix
-        self.qkv_bias, self.out_bias, self.window = bool(qkv_bias), bool(out_bias), int(window)
-        self.rotary = (positions or {}).get(position) if position else None
-        if position and self.rotary is None:
-            raise UnsupportedError(f"attention names position encoding '{position}', which the plan does not define")
-        n = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj"}
-        n.update(names or {})
-        self.names = {k: f"{prefix}.{v}" for k, v in n.items()}
-        self.scale = 1.0 / math.sqrt(self.d) if scale is None else float(scale)
-        self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
-
-    @property
-    def QD(self):
-        return self.H * self.d
-
-    @property
-    def KD(self):
-        return self.G * self.d
-
-    @property
-    def VD(self):
-        return self.G * self.dv
-
-    @property
-    def OD(self):
-        return self.H * self.dv
-
-    def cache_spec(self):
-        return CacheSpec(self.G, self.d, self.window, 0 if self.dv == self.d else self.dv)
-
-    def step_arrays_key(self):
-        return ("paged_attention_tiles", self.H // self.G)
-
-    def step_arrays(self, batch):
-        # the tile lists of the attention kernels: how they cut the step's tokens is the kernels' business
-        return kernels.attention_step_arrays(batch.q_lens, self.H // self.G)
-
-    def _projections(self):
-        """(key of ``names``, output features) of the projections in the fused product's row order."""
-        return [("q", self.QD)] + ([("k", self.KD), ("v", self.VD)] if self.own_kv else [])
-
-    def tensor_specs(self):
-        s = [TensorSpec(self.names[x] + self.wsuf, (n, self.E)) for x, n in self._projections()]
-        s.append(TensorSpec(self.names["o"] + self.wsuf, (self.E, self.OD)))
-        if self.qkv_bias:
-            s += [TensorSpec(self.names[x] + self.bsuf, (n,)) for x, n in self._projections()]
-        if self.out_bias:
-            s.append(TensorSpec(self.names["o"] + self.bsuf, (self.E,)))
-        return s
-
-    def bind(self, tensors, run_dtype, device):
-        # q, k and v rows go straight into the one matrix the product reads, a tensor at a time
-        self.w_qkv = fused_rows(tensors, [self.names[x] + self.wsuf for x, _ in self._projections()], device)
-        if self.qkv_bias:
-            self.b_qkv = fused_rows(tensors, [self.names[x] + self.bsuf for x, _ in self._projections()], device)
-        self.w_o = tensors[self.names["o"] + self.wsuf].contiguous()
-        if self.out_bias:
-            self.b_o = tensors[self.names["o"] + self.bsuf].contiguous()
-
-    def weight_bytes(self):
-        return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.b_qkv, self.w_o, self.b_o)
-                   if w is not None)
-
-    def flops(self, q_lens, kv_lens):
-        T = sum(q_lens)
-        seen = 0                        # (query, key) pairs: token i of n new ones over a history of m sees m - n + i + 1
-        for n, m in zip(q_lens, kv_lens):
-            for_all = n * (m - n) + n * (n + 1) // 2
-            if self.window > 0:
-                for_all = sum(min(self.window, m - n + i + 1) for i in range(n)) if m > self.window else for_all
-            seen += for_all
-        return 2.0 * T * (self.w_qkv.numel() + self.w_o.numel()) + 2.0 * (self.QD + self.OD) * seen
-
-    def _attend(self, ctx, xn, cache, write_cache):
-        T = xn.shape[0]
-        q = ctx.buf("attn_q", (T, self.QD), xn.dtype)
-        meta = ctx.group_meta(cache.group)
-        cos_sin = self.rotary.cos_sin if self.rotary is not None else None
-        n_rot = self.rotary.n_rot if self.rotary is not None else 0
-        if write_cache and not self.own_kv:
-            raise ValueError("a layer without key and value projections must read another schedule entry's cache")
-        if self.general:
-            # the product's sums stay float32 until rotation and the heads' normalisation are done
-            G = self.G if self.own_kv else 0
-            qkv = ctx.buf("attn_qkv32", (T, self.QD + G * (self.d + self.dv)), torch.float32)
-            with kernels.phase("qkv"):
-                kernels.linear_rope_norm_kv(xn, self.w_qkv, self.b_qkv, qkv, cos_sin, n_rot, ctx.positions,
-                                            meta.slots if write_cache else None, q, cache.k, cache.v, self.H, G, self.d,
-                                            self.dv, self.qk_norm_eps)
-        else:
-            qkv = ctx.buf("attn_qkv", (T, self.QD + 2 * self.KD), xn.dtype)
-            with kernels.phase("qkv"):
-                kernels.linear_rope_kv(xn, self.w_qkv, self.b_qkv, qkv, cos_sin, n_rot, ctx.positions,
-                                       meta.slots if write_cache else None, q, cache.k, cache.v, self.H, self.G, self.d)
-        att = ctx.buf("attn_out", (T, self.OD), xn.dtype)
-        with kernels.phase("attn"):
-            kernels.paged_attention(q, cache.k, cache.v, meta, ctx, self.H, self.G, self.d,
-                                    self.window, self.scale, att, tiles=ctx.arrays(self.step_arrays_key()), dv=self.dv)
-        return att
+class OutputProduct:
+    """What mixers that end in one product over the concatenated heads share: ``self._attend(ctx, xn, cache,
+    write_cache)`` gives the heads' outputs, ``self.w_o`` / ``self.b_o`` carry them back to the stream."""
 
     def forward(self, ctx, xn, residual, cache, state, write_cache, accumulate=True):
         """``accumulate=False`` stores the sublayer's output in ``residual`` (float32) instead of adding it."""
@@ -167,6 +57,160 @@ class PagedAttention(Mixer):
         with kernels.phase("wo"):
             kernels.linear_residual_norm(att, self.w_o, self.b_o, residual, args[0], args[1], out)
         return True
+
+
+class PagedAttention(OutputProduct, Mixer):
+    graph_safe = True
+    V_FIRST = "attn_v_first"          # the scratch buffer in which a step's first value-mixing layer leaves its values
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 qkv_bias: bool, out_bias: bool, window: int, position, prefix: str,
+                 positions=None, names=None, scale=None, v_head_dim=None, qk_norm_eps=None, own_kv: bool = True,
+                 bias_suffix: str = ".bias", weight_suffix: str = ".weight", qk_norm_weights=None, chunk: int = 0,
+                 v_mix=None, v_mix_tensor: str = "vmix", **_):
+        self.E, self.H, self.G, self.d = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
+        if self.H % self.G:
+            raise UnsupportedError(f"unsupported attention geometry: {self.H} heads over {self.G} key/value heads")
+        self.dv = int(v_head_dim) if v_head_dim else self.d
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        self.own_kv = bool(own_kv)
+        # the q|k|v tail that normalises heads also takes the other two options; the reference's layer keeps its own
+        self.chunk = int(chunk or 0)
+        if v_mix not in (None, "first", "later"):
+            raise UnsupportedError(f"v_mix '{v_mix}' is not known (first, later)")
+        self.v_mix = v_mix
+        if self.v_mix and not self.own_kv:
+            raise UnsupportedError("a layer without values of its own cannot mix them")
+        if qk_norm_weights and self.qk_norm_eps is None:
+            raise UnsupportedError("weights on the query and key norm need that norm (qk_norm_eps)")
+        self.general = (self.qk_norm_eps is not None or self.dv != self.d or not self.own_kv or self.v_mix is not None)
+        if self.general:
+            if not (0 < self.d <= kernels.MAX_HEAD_DIM and 0 < self.dv <= kernels.MAX_HEAD_DIM):
+                raise UnsupportedError(f"head sizes {self.d} / {self.dv} are not supported (1 to {kernels.MAX_HEAD_DIM})")
+        else:
+            kernels.check_head_dim(self.d)
+        self.wsuf, self.bsuf = weight_suffix, bias_suffix
+        self.qkv_bias, self.out_bias, self.window = bool(qkv_bias), bool(out_bias), int(window)
+        self.mask = kernels.mask_code(self.window, self.chunk)
+        self.rotary = (positions or {}).get(position) if position else None
+        if position and self.rotary is None:
+            raise UnsupportedError(f"attention names position encoding '{position}', which the plan does not define")
+        if self.rotary is not None and getattr(self.rotary, "pairing", "half") != "half":
+            raise UnsupportedError("this attention rotates pairs (i, i + n_rot/2) only")
+        n = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj"}
+        n.update(names or {})
+        self.names = {k: f"{prefix}.{v}" for k, v in n.items()}
+        self.norm_names = {k: f"{prefix}.{v}" for k, v in (qk_norm_weights or {}).items()}
+        if self.norm_names and set(self.norm_names) != {"q", "k"}:
+            raise UnsupportedError("qk_norm_weights names one weight for q and one for k")
+        self.v_mix_name = f"{prefix}.{v_mix_tensor}" if self.v_mix else None
+        self.scale = 1.0 / math.sqrt(self.d) if scale is None else float(scale)
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+        self.norm_w = None              # (q weight, k weight), float32
+        self.v_lambda = 0.0
+
+    @property
+    def QD(self):
+        return self.H * self.d
+
+    @property
+    def KD(self):
+        return self.G * self.d
+
+    @property
+    def VD(self):
+        return self.G * self.dv
+
+    @property
+    def OD(self):
+        return self.H * self.dv
+
+    def cache_spec(self):
+        return CacheSpec(self.G, self.d, self.window, 0 if self.dv == self.d else self.dv, chunk=self.chunk)
+
+    def step_arrays_key(self):
+        return ("paged_attention_tiles", self.H // self.G)
+
+    def step_arrays(self, batch):
+        # the tile lists of the attention kernels: how they cut the step's tokens is the kernels' business
+        return kernels.attention_step_arrays(batch.q_lens, self.H // self.G)
+
+    def _projections(self):
+        """(key of ``names``, output features) of the projections in the fused product's row order."""
+        return [("q", self.QD)] + ([("k", self.KD), ("v", self.VD)] if self.own_kv else [])
+
+    def tensor_specs(self):
+        s = [TensorSpec(self.names[x] + self.wsuf, (n, self.E)) for x, n in self._projections()]
+        s.append(TensorSpec(self.names["o"] + self.wsuf, (self.E, self.OD)))
+        if self.qkv_bias:
+            s += [TensorSpec(self.names[x] + self.bsuf, (n,)) for x, n in self._projections()]
+        if self.out_bias:
+            s.append(TensorSpec(self.names["o"] + self.bsuf, (self.E,)))
+        s += [TensorSpec(self.norm_names[x], (self.d,), init="norm") for x in sorted(self.norm_names)]
+        if self.v_mix_name:
+            s.append(TensorSpec(self.v_mix_name, (), init="half"))       # the first layer's is stored too, and unused
+        return s
+
+    def bind(self, tensors, run_dtype, device):
+        # q, k and v rows go straight into the one matrix the product reads, a tensor at a time
+        self.w_qkv = fused_rows(tensors, [self.names[x] + self.wsuf for x, _ in self._projections()], device)
+        if self.qkv_bias:
+            self.b_qkv = fused_rows(tensors, [self.names[x] + self.bsuf for x, _ in self._projections()], device)
+        self.w_o = tensors[self.names["o"] + self.wsuf].contiguous()
+        if self.out_bias:
+            self.b_o = tensors[self.names["o"] + self.bsuf].contiguous()
+        if self.norm_names:
+            self.norm_w = tuple(tensors[self.norm_names[x]].to(torch.float32).contiguous() for x in ("q", "k"))
+        if self.v_mix_name:
+            lam = tensors[self.v_mix_name]
+            self.v_lambda = float(lam.to(torch.float32).reshape(-1)[0].item()) if self.v_mix == "later" else 0.0
+
+    def weight_bytes(self):
+        return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.b_qkv, self.w_o, self.b_o)
+                   if w is not None)
+
+    def flops(self, q_lens, kv_lens):
+        T = sum(q_lens)
+        seen = 0                        # (query, key) pairs: token i of n new ones over a history of m sees m - n + i + 1
+        for n, m in zip(q_lens, kv_lens):
+            for_all = n * (m - n) + n * (n + 1) // 2
+            if self.window > 0:
+                for_all = sum(min(self.window, m - n + i + 1) for i in range(n)) if m > self.window else for_all
+            elif self.chunk > 0:
+                for_all = sum((m - n + i) % self.chunk + 1 for i in range(n))
+            seen += for_all
+        return 2.0 * T * (self.w_qkv.numel() + self.w_o.numel()) + 2.0 * (self.QD + self.OD) * seen
+
+    def _attend(self, ctx, xn, cache, write_cache):
+        T = xn.shape[0]
+        q = ctx.buf("attn_q", (T, self.QD), xn.dtype)
+        meta = ctx.group_meta(cache.group)
+        cos_sin = self.rotary.cos_sin if self.rotary is not None else None
+        n_rot = self.rotary.n_rot if self.rotary is not None else 0
+        if write_cache and not self.own_kv:
+            raise ValueError("a layer without key and value projections must read another schedule entry's cache")
+        if self.general:
+            # the product's sums stay float32 until rotation and the heads' normalisation are done
+            G = self.G if self.own_kv else 0
+            qkv = ctx.buf("attn_qkv32", (T, self.QD + G * (self.d + self.dv)), torch.float32)
+            mix = None
+            if self.v_mix:
+                first = ctx.buf(self.V_FIRST, (T, self.VD), torch.float32)
+                mix = (first, 1 if self.v_mix == "first" else 2, self.v_lambda)
+            with kernels.phase("qkv"):
+                kernels.linear_rope_norm_kv(xn, self.w_qkv, self.b_qkv, qkv, cos_sin, n_rot, ctx.positions,
+                                            meta.slots if write_cache else None, q, cache.k, cache.v, self.H, G, self.d,
+                                            self.dv, self.qk_norm_eps, norm_weights=self.norm_w, value_mix=mix)
+        else:
+            qkv = ctx.buf("attn_qkv", (T, self.QD + 2 * self.KD), xn.dtype)
+            with kernels.phase("qkv"):
+                kernels.linear_rope_kv(xn, self.w_qkv, self.b_qkv, qkv, cos_sin, n_rot, ctx.positions,
+                                       meta.slots if write_cache else None, q, cache.k, cache.v, self.H, self.G, self.d)
+        att = ctx.buf("attn_out", (T, self.OD), xn.dtype)
+        with kernels.phase("attn"):
+            kernels.paged_attention(q, cache.k, cache.v, meta, ctx, self.H, self.G, self.d,
+                                    self.mask, self.scale, att, tiles=ctx.arrays(self.step_arrays_key()), dv=self.dv)
+        return att
 
 
 register_part("mixer", "paged_attention", PagedAttention)

@@ -45,16 +45,30 @@ def make_part(category: str, spec: PartSpec, **context: Any) -> "Part":
 @dataclass(frozen=True)
 class CacheSpec:
     """What a mixer asks of the paged cache: per token ``num_kv_heads * (head_dim + value_dim)`` values
-    (keys then values); ``window`` = 0 keeps every key, else only the most recent ``window``;
-    ``v_head_dim`` = 0 means value heads as wide as key heads."""
+    (keys then values); ``window`` = 0 keeps every key, else only the most recent ``window``; ``chunk`` > 0: a query
+    sees the keys of its own chunk of that many positions only (chunks counted from position 0), so pages of earlier
+    chunks are kept no longer; ``v_head_dim`` = 0 means value heads as wide as key heads; ``values_in_keys``: there is
+    no array of values at all (a value is a leading part of its key: latent rows)."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: int = 0
+    chunk: int = 0
+    values_in_keys: bool = False
 
     @property
     def value_dim(self) -> int:
+        if self.values_in_keys:
+            return 0
         return self.v_head_dim or self.head_dim
+
+    def first_visible(self, pos: int) -> int:
+        """The first key a query at ``pos`` sees; never decreases as ``pos`` grows."""
+        if self.window > 0:
+            return max(0, pos - self.window + 1)
+        if self.chunk > 0:
+            return pos // self.chunk * self.chunk
+        return 0
 
 
 @dataclass(frozen=True)
@@ -65,6 +79,7 @@ class StateSpec:
 
 
 class Part:
+    # (an embedding may declare per-request state too: ``state_spec()``, as mixers do)
     # True when forward() only launches kernels on tensors at stable addresses and reads nothing of the step
     # on the host, so that a decode step may be captured once as a CUDA graph and replayed
     graph_safe = False

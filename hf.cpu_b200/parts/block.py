@@ -20,6 +20,16 @@ class PreNormResidual(Block):
             norm1.forward(x, xn)
         else:
             xn = xn_ready
+        if ffn is None:
+            # a layer that is a mixer only: the norm behind its product is the next block's first
+            fused = getattr(mixer, "forward_then_norm", None) if next_norm is not None else None
+            if not fused:
+                mixer.forward(ctx, xn, x, cache, state, write_cache)
+                return None
+            nxt = ctx.buf("block_xn", x.shape, ctx.run_dtype)       # (xn may live there: the mixer has read it by then)
+            if not fused(ctx, xn, x, cache, state, write_cache, next_norm, nxt):
+                next_norm.forward(x, nxt)
+            return nxt
         xn2 = ctx.buf("block_xn2", x.shape, ctx.run_dtype)
         fused = getattr(mixer, "forward_then_norm", None)
         if not (fused and fused(ctx, xn, x, cache, state, write_cache, norm2, xn2)):

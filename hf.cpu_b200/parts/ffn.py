@@ -72,5 +72,62 @@ class SwiGlu(FeedForward):
         return True
 
 
+class Mlp(FeedForward):
+    """The feed-forward without a gate: ``down(act(up x))``; ``activation`` as the product kernels name them (``relu2``
+    is the square of relu).  The activation runs in the up product's epilogue, the down product ends in the sum with the
+    stream and the following norm, as the gated form's does."""
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str, activation: str = "relu2", names=None, **_):
+        self.E, self.F = int(hidden_size), int(intermediate_size)
+        if activation not in kernels.ACTIVATIONS or activation == "none":
+            raise UnsupportedError(f"feed-forward: activation '{activation}' is not supported")
+        self.activation = activation
+        n = {"up": "up", "down": "down"}
+        n.update(names or {})
+        self.names = {k: f"{prefix}.{v}" for k, v in n.items()}
+        self.w_up = self.w_down = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.names["up"], (self.F, self.E)), TensorSpec(self.names["down"], (self.E, self.F))]
+
+    def bind(self, tensors, run_dtype, device):
+        self.w_up = tensors[self.names["up"]].contiguous()
+        self.w_down = tensors[self.names["down"]].contiguous()
+
+    def weight_bytes(self):
+        return sum(w.numel() * w.element_size() for w in (self.w_up, self.w_down))
+
+    def flops(self, rows):
+        return 2.0 * rows * (self.w_up.numel() + self.w_down.numel())
+
+    def _hidden(self, ctx, xn):
+        h = ctx.buf("ffn_h", (xn.shape[0], self.F), xn.dtype)
+        with kernels.phase("gate_up"):
+            kernels.linear_act(xn, self.w_up, h, self.activation)
+        return h
+
+    def forward(self, ctx, xn, residual, accumulate=True):
+        h = self._hidden(ctx, xn)
+        with kernels.phase("down"):
+            kernels.linear(h, self.w_down, None, residual, accumulate=accumulate)
+
+    def forward_into_norm(self, ctx, xn, y_buf, residual, post, next_norm, out):
+        h = self._hidden(ctx, xn)
+        with kernels.phase("down"):
+            return post.add_product_into(h, self.w_down, None, y_buf, residual, next_norm, out)
+
+    def forward_then_norm(self, ctx, xn, residual, norm, out):
+        args = norm.fused_args()
+        if args is None:
+            self.forward(ctx, xn, residual)
+            return False
+        h = self._hidden(ctx, xn)
+        with kernels.phase("down"):
+            kernels.linear_residual_norm(h, self.w_down, None, residual, args[0], args[1], out)
+        return True
+
+
+register_part("ffn", "mlp", Mlp)
 register_part("ffn", "swiglu", SwiGlu)
 register_part("ffn", "gated", SwiGlu)               # the same part under the name that does not fix the activation

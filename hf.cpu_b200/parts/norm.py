@@ -11,17 +11,23 @@ from .base import Norm, register_part
 
 
 class RmsNorm(Norm):
+    """``offset`` is added to the stored weight: a weight stored around zero (``x / rms * (1 + w)``) has offset 1.  The
+    sum is made once, in float32, when the weights are bound; every kernel that applies this norm then reads a float32
+    weight (1 + w has more digits than bfloat16 keeps)."""
     graph_safe = True
 
-    def __init__(self, size: int, eps: float, tensor: str, **_):
-        self.size, self.eps, self.tensor = int(size), float(eps), tensor
+    def __init__(self, size: int, eps: float, tensor: str, offset: float = 0.0, **_):
+        self.size, self.eps, self.tensor, self.offset = int(size), float(eps), tensor, float(offset)
         self.weight = None
 
     def tensor_specs(self):
-        return [TensorSpec(self.tensor, (self.size,), init="norm")]
+        # random weights are drawn around the value that makes the norm's factor about one
+        return [TensorSpec(self.tensor, (self.size,), init="normal" if self.offset else "norm")]
 
     def bind(self, tensors, run_dtype, device):
         self.weight = tensors[self.tensor].contiguous()
+        if self.offset:
+            self.weight = (self.weight.to(torch.float32) + self.offset).contiguous()
 
     def fused_args(self):
         return self.weight, self.eps

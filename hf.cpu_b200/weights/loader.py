@@ -57,7 +57,7 @@ class WeightError(ValueError):
 class TensorSpec:
     name: str
     shape: Tuple[int, ...]
-    init: str = "normal"        # "normal": N(0, std); "norm": 1 + N(0, std/2); "int": small integers
+    init: str = "normal"        # "normal": N(0, std); "norm": 1 + N(0, std/2); "half": 0.5 + N(0, std/2); "int": small integers
     optional: bool = False
 
 

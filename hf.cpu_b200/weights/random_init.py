@@ -1,6 +1,6 @@
 """Random weights from a configuration and a seed.
 
-Matrices and biases are N(0, std), norm weights 1 + N(0, std/2).  Each tensor
+Matrices and biases are N(0, std), norm weights 1 + N(0, std/2), mixing weights 0.5 + N(0, std/2).  Each tensor
 has its own generator keyed by the seed and the tensor's name, so the values do
 not depend on the order of creation.  The reference's generator for its tests is
 tools/mkmodel.pl (seeded, per-tensor scales, tools/mkmodel.pl:104-119).
@@ -29,7 +29,7 @@ def _draw(s: TensorSpec, seed: int, dtype: torch.dtype, device: torch.device, st
         return torch.randint(0, 8, s.shape, generator=g, device=device, dtype=torch.int32)
     # drawn in float32 on the target device
     t = torch.empty(s.shape, dtype=torch.float32, device=device).normal_(0.0, 1.0, generator=g)
-    t = 1.0 + t * (std / 2) if s.init == "norm" else t * std
+    t = 1.0 + t * (std / 2) if s.init == "norm" else (0.5 + t * (std / 2) if s.init == "half" else t * std)
     return t.to(dtype)
 
 

@@ -14,6 +14,20 @@ class EmuBackend:
     def embed(self, ids, table, out):
         out.copy_(table[ids.long()].float())
 
+    def embed_pair(self, ids, table, scale, pair, buckets, mul_prev, mul_cur, ctx, prev_state, out):
+        x = table[ids.long()].float() * scale
+        if pair is not None:
+            toks, cu, slots = ids.tolist(), ctx.cu_tokens.tolist(), ctx.seq_slots.tolist()
+            rows = []
+            for s in range(len(slots)):
+                prev = int(prev_state[slots[s]]) - 1
+                for t in range(cu[s], cu[s + 1]):
+                    rows.append(buckets if prev < 0 else (prev * mul_prev + toks[t] * mul_cur) % buckets)
+                    prev = toks[t]
+                prev_state[slots[s]] = prev + 1
+            x = x + pair[torch.tensor(rows, device=ids.device)].float()
+        out.copy_(x)
+
     def rmsnorm(self, x, w, eps, out, rows):
         xr = x if rows is None else x[rows.long()]
         r = 1.0 / torch.sqrt((xr * xr).sum(-1, keepdim=True) / xr.shape[-1] + eps)
@@ -52,13 +66,14 @@ class EmuBackend:
         T = q.shape[0]
         bs = meta.block_size
         dv = d if dv is None else dv
-        kf, vf = k_cache.reshape(-1, G, d).float(), v_cache.reshape(-1, G, dv).float()
+        kf = k_cache.reshape(-1, G, d).float()
+        vf = v_cache.reshape(-1, G, dv).float() if v_cache is not None else kf[..., :dv]      # a value inside its key
         seqs, poss, table = ctx.token_seq.tolist(), ctx.positions.tolist(), meta.block_table.tolist()
         qf = q.float().view(T, H, d)
         res = torch.zeros(T, H, dv, dtype=torch.float32, device=q.device)
         for t in range(T):
             pos, row = poss[t], table[seqs[t]]
-            lo = max(0, pos - window + 1) if window > 0 else 0
+            lo = max(0, pos - window + 1) if window > 0 else (pos // -window * -window if window < 0 else 0)
             idx = []
             for j in range(lo, pos + 1):
                 page = row[j // bs]
@@ -118,11 +133,11 @@ class EmuBackend:
         self.dyt_residual(y_buf, post, residual, nxt, out, mix=mix)
 
     def linear_rope_norm_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d, dv,
-                            norm_eps):
+                            norm_eps, norm_weights=None, value_mix=None):
         self.linear(a, w, bias, qkv_buf, False)
         T = a.shape[0]
 
-        def finish(v):                                 # [T, heads, d]
+        def finish(v, weight=None):                    # [T, heads, d]
             if n_rot:
                 half = n_rot // 2
                 cs = cos_sin[positions.long()]
@@ -131,15 +146,60 @@ class EmuBackend:
                 v = torch.cat([x * c - y * s, x * s + y * c, v[..., n_rot:]], -1)
             if norm_eps is not None:
                 v = v / torch.sqrt((v * v).mean(-1, keepdim=True) + norm_eps)
+                if weight is not None:
+                    v = v * weight
             return v
-        q_out.copy_(finish(qkv_buf[:, :H * d].view(T, H, d)).reshape(T, H * d).to(q_out.dtype))
+        qw, kw = norm_weights or (None, None)
+        q_out.copy_(finish(qkv_buf[:, :H * d].view(T, H, d), qw).reshape(T, H * d).to(q_out.dtype))
         if not G or slots is None:
             return
         ok = slots >= 0
-        k = finish(qkv_buf[:, H * d:(H + G) * d].view(T, G, d))
+        k = finish(qkv_buf[:, H * d:(H + G) * d].view(T, G, d), kw)
         v = qkv_buf[:, (H + G) * d:].view(T, G, dv)
+        if value_mix is not None:
+            first, mode, lam = value_mix
+            if mode == 1:
+                first.copy_(v.reshape(T, G * dv))
+            else:
+                v = (1.0 - lam) * v + lam * first.view(T, G, dv)
         k_cache.view(-1, G, d)[slots[ok].long()] = k[ok].to(k_cache.dtype)
         v_cache.view(-1, G, dv)[slots[ok].long()] = v[ok].to(v_cache.dtype)
+
+    @staticmethod
+    def _rotate_pairs(v, cos_sin, positions):
+        """Pairs (2i, 2i + 1) of the last axis, all of it."""
+        cs = cos_sin[positions.long()]
+        c, s = cs[..., 0], cs[..., 1]
+        while c.dim() < v.dim():
+            c, s = c.unsqueeze(1), s.unsqueeze(1)
+        a, b = v[..., 0::2], v[..., 1::2]
+        return torch.stack([a * c - b * s, a * s + b * c], -1).flatten(-2)
+
+    def linear_latent_split(self, a, w, buf, q_norm_w, kv_norm_w, eps, cos_sin, positions, slots, cq_out, cache, q_rank, kv_rank, rot):
+        self.linear(a, w, None, buf, False)
+        unit = lambda v: v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
+        cq_out.copy_((unit(buf[:, :q_rank]) * q_norm_w).to(cq_out.dtype))
+        c = unit(buf[:, q_rank:q_rank + kv_rank]) * kv_norm_w
+        r = buf[:, q_rank + kv_rank:]
+        if rot:
+            r = self._rotate_pairs(r, cos_sin, positions)
+        if slots is None:
+            return
+        ok = slots >= 0
+        cache.view(-1, kv_rank + rot)[slots[ok].long()] = torch.cat([c, r], -1)[ok].to(cache.dtype)
+
+    def linear_latent_query(self, a, w, buf, cos_sin, positions, q_plain, q_att, H, d, rot, att_col):
+        self.linear(a, w, None, buf, False)
+        T = a.shape[0]
+        q = buf.view(T, H, d + rot)
+        q_plain.copy_(q[..., :d].reshape(T, H * d).to(q_plain.dtype))
+        if rot:
+            q_att.view(T, H, -1)[..., att_col:att_col + rot] = self._rotate_pairs(q[..., d:], cos_sin, positions).to(q_att.dtype)
+
+    def headwise_linear(self, x, w, out, H, in_row, out_row):
+        T, (_, N, K) = x.shape[0], w.shape
+        y = torch.einsum("thk,hnk->thn", x.view(T, H, in_row)[..., :K].float(), w.float())
+        out.view(T, H, out_row)[..., :N] = y.to(out.dtype)
 
     @staticmethod
     def _activate(z, act):

@@ -72,8 +72,16 @@ def test_rotary_part_table():
     assert rot.cos_sin.shape == (300, 16, 2)
     assert float((rot.cos_sin[..., 0].double() - cos).abs().max()) < 1e-7
     assert float((rot.cos_sin[..., 1].double() - sin).abs().max()) < 1e-7
+    # the table does not depend on the pairing; a mixer takes the pairings its kernels know
+    inter = make_part("position", PartSpec("rotary", {"head_dim": 48, "n_rot": 32, "theta": 12345.0, "pairing": "interleaved"}))
+    inter.prepare(300, torch.device("cpu"))
+    assert torch.equal(inter.cos_sin, rot.cos_sin)
     with pytest.raises(UnsupportedError):
-        make_part("position", PartSpec("rotary", {"head_dim": 48, "n_rot": 32, "theta": 1.0, "pairing": "interleaved"}))
+        make_part("mixer", PartSpec("paged_attention", {"hidden_size": 64, "num_heads": 2, "num_kv_heads": 2, "head_dim": 48,
+                                                        "qkv_bias": False, "out_bias": False, "window": 0, "position": "r",
+                                                        "prefix": "a"}), positions={"r": inter})
+    with pytest.raises(UnsupportedError):
+        make_part("position", PartSpec("rotary", {"head_dim": 48, "n_rot": 32, "theta": 1.0, "pairing": "quarter"}))
     with pytest.raises(UnsupportedError):
         make_part("position", PartSpec("rotary", {"head_dim": 16, "n_rot": 32, "theta": 1.0}))
 
