@@ -184,6 +184,14 @@ def mask_code(window: int = 0, chunk: int = 0) -> int:
     return window if window else -chunk
 
 
+def tiled_attention_takes(dtype, head_dim: int, block_size: int) -> bool:
+    """Whether the tiled tensor-core attention kernels serve heads of this type and size (with value heads of the same
+    size) from pages of ``block_size`` tokens; everything else goes to the plain kernel."""
+    b = backend()
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and 64 % int(block_size) == 0
+            and getattr(b, "attention", "plain") == "fast")
+
+
 def paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tiles=None, dv=None, values_in_keys=False) -> None:
     """``window``: a :func:`mask_code`.  ``tiles``: the device arrays of :func:`attention_step_arrays` for this step
     (without them only the plain kernel runs).  ``dv``: the size of a value head where it is not ``d``; ``out`` is then

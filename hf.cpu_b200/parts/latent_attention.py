@@ -13,6 +13,10 @@ Per token, with h the mixer's input:
   of its key: ``score = ([Wuk_h^T q_plain | q_rot] . [c | r]) * scale``, ``out_h = Wuv_h (sum_j p_j c_j)``.
 * ``out = concat(out_h) W_o^T`` is added to the residual.
 
+Where the cached row has a size the tiled tensor-core attention kernels take (they want value heads as wide as key
+heads), the whole row serves as the value: the rotated columns of the weighted sum are computed and not read.  Other
+sizes take the plain kernel, which reads a value as the first ``kv_rank`` elements of its key.
+
 The mask is a sliding window (``window`` > 0) or causal (0).  The rotation pairs dimensions (2i, 2i + 1) and takes its
 table from a shared position encoding (which may be scaled for long contexts).  The reference has no such layer; the
 nearest thing in it is the grouped attention of src/model.c:581-609.
@@ -56,6 +60,12 @@ class LatentAttention(OutputProduct, Mixer):
 
     def cache_spec(self):
         return CacheSpec(1, self.row, self.window, values_in_keys=True)
+
+    def step_arrays_key(self):
+        return ("paged_attention_tiles", self.H)            # all heads share the one cached row: one group of H heads
+
+    def step_arrays(self, batch):
+        return kernels.attention_step_arrays(batch.q_lens, self.H)
 
     def tensor_specs(self):
         n = self.names
@@ -107,13 +117,19 @@ class LatentAttention(OutputProduct, Mixer):
             kernels.linear_latent_query(cq, self.w_uq, q32, cos_sin, ctx.positions, q_plain, q_att, self.H, self.d, self.dr,
                                         self.R)
             kernels.headwise_linear(q_plain, self.w_ukt, q_att, self.H, self.d, self.row)
-        lat = ctx.buf("lat_out", (T, self.H * self.R), dt)
+        whole_row = kernels.tiled_attention_takes(dt, self.row, meta.block_size)
+        out_row = self.row if whole_row else self.R
+        lat = ctx.buf("lat_out", (T, self.H * out_row), dt)
         with kernels.phase("attn"):
-            kernels.paged_attention(q_att, cache.k, None, meta, ctx, self.H, 1, self.row, kernels.mask_code(self.window),
-                                    self.scale, lat, dv=self.R, values_in_keys=True)
+            if whole_row:
+                kernels.paged_attention(q_att, cache.k, cache.k, meta, ctx, self.H, 1, self.row, kernels.mask_code(self.window),
+                                        self.scale, lat, tiles=ctx.arrays(self.step_arrays_key()))
+            else:
+                kernels.paged_attention(q_att, cache.k, None, meta, ctx, self.H, 1, self.row, kernels.mask_code(self.window),
+                                        self.scale, lat, dv=self.R, values_in_keys=True)
         att = ctx.buf("lat_heads", (T, self.H * self.dv), dt)
         with kernels.phase("attn"):
-            kernels.headwise_linear(lat, self.w_uv, att, self.H, self.R, self.dv)
+            kernels.headwise_linear(lat, self.w_uv, att, self.H, out_row, self.dv)
         return att
 
 

@@ -205,3 +205,13 @@ def forward(cfg, W, ids, layers_out=None):
         if layers_out is not None:
             layers_out.append(x.copy())
     return norm_one_plus(x, W["final.norm"], eps) @ W["head"].T
+
+
+def greedy(cfg, W, prompt, n):
+    """n tokens by arg-max, the whole sequence computed anew for each."""
+    ids, out = list(prompt), []
+    for _ in range(n):
+        t = int(np.argmax(forward(cfg, W, ids)[-1]))
+        out.append(t)
+        ids.append(t)
+    return out
