@@ -44,10 +44,10 @@ ODD = model(211, 72, 1e-5, 3.0, (53, 31, 7), [
 ])
 # Sizes the tensor-core kernels take: head sizes 64 and 128 with equal value heads, a latent row of 128 and one of 64,
 # widths that are multiples of 8.
-WIDE = model(1032, 256, 1e-6, 8.0, (509, 127, 17), [
-    layer(lat(4, 64, 32, 64, 128, 96, 0.12, 40, 20000.0, scaling=(8.0, 256, 32.0, 1.0)), 512),
+WIDE = model(1032, 256, 1e-6, 8.0, (499, 131, 19), [
+    layer(lat(4, 64, 32, 64, 128, 96, 0.12, 44, 25000.0, scaling=(6.0, 128, 16.0, 1.0)), 512),
     layer(att(8, 2, 64, 64, 0.15, 48, v_mix=True), 256),
-    layer(att(4, 1, 128, 128, 0.1, 200), 512),
+    layer(att(4, 1, 128, 128, 0.1, 208), 512),
     layer(lat(8, 32, 16, 48, 64, 48, 0.15, 100, 10000.0), 256),
     layer(att(8, 2, 64, 64, 0.15, 150, v_mix=True), 256),
 ])

@@ -51,7 +51,7 @@ def table(rot, n):
 
 # ---- each mechanism alone ---------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("pair", [(53, 31, 7), (1, 5, 3), (509, 100003, 99991), None])
+@pytest.mark.parametrize("pair", [(53, 31, 7), (1, 5, 3), (499, 100003, 99991), None])
 def test_embedding_with_scale_and_pair_term(dtype, pair):
     """Three steps over two slots: a first step with a whole prompt beside a single first token, a step of single tokens,
     and a request that takes over a freed slot and must start without a previous token."""
@@ -109,7 +109,7 @@ def test_norm_with_weight_stored_around_zero(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("geom", [(6, 3, 24, 40), (8, 8, 48, 64), (2, 1, 20, 12), (8, 2, 64, 64), (4, 1, 128, 128), (1, 1, 256, 8)])
+@pytest.mark.parametrize("geom", [(6, 3, 24, 40), (5, 5, 48, 56), (2, 1, 20, 12), (8, 2, 64, 64), (4, 1, 128, 128), (1, 1, 256, 8)])
 def test_head_norms_with_weights_and_value_mixing(dtype, geom):
     """The q|k|v tail without rotation: queries and keys normed per head with a weight shared by the heads; the first mixing
     layer leaves its values behind, a later one stores the mixture."""
@@ -145,7 +145,7 @@ def test_head_norms_with_weights_and_value_mixing(dtype, geom):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("geom", [(3, 16, 8, 24, 40, 24), (4, 32, 32, 80, 128, 64), (5, 8, 12, 20, 16, 36), (1, 6, 2, 10, 12, 10),
+@pytest.mark.parametrize("geom", [(3, 16, 8, 24, 40, 24), (4, 32, 16, 72, 112, 64), (5, 8, 12, 20, 16, 36), (1, 6, 2, 10, 12, 10),
                                   (4, 64, 32, 64, 128, 96), (2, 128, 64, 128, 1536, 512)])
 def test_latent_tails_and_per_head_products(dtype, geom):
     """Down product -> two norms, rotation in pairs (2i, 2i+1), cache row; query product -> plain parts and rotated parts;
@@ -243,7 +243,7 @@ MASKS = {"window": lambda size: (size, lambda pos: max(0, pos - size + 1)),
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("kind,size", [("window", 40), ("window", 1), ("chunk", 200), ("chunk", 16), ("chunk", 1), ("window", 7)])
+@pytest.mark.parametrize("kind,size", [("window", 44), ("window", 1), ("chunk", 208), ("chunk", 16), ("chunk", 1), ("window", 7)])
 @pytest.mark.parametrize("geom", [(6, 3, 24, 40, False), (4, 1, 96, 64, True), (3, 1, 32, 24, True), (2, 1, 576, 512, True)])
 def test_edges_of_windows_and_chunks_plain_kernel(dtype, kind, size, geom):
     """One key carries a score far above the rest; it is placed just inside and just outside the mask of the last query
@@ -289,7 +289,7 @@ def test_edges_of_windows_and_chunks_plain_kernel(dtype, kind, size, geom):
     K().check_device_errors()
 
 
-@pytest.mark.parametrize("kind,size", [("window", 40), ("window", 100), ("chunk", 48), ("chunk", 200), ("chunk", 64), ("chunk", 1)])
+@pytest.mark.parametrize("kind,size", [("window", 44), ("window", 100), ("chunk", 48), ("chunk", 208), ("chunk", 64), ("chunk", 1)])
 @pytest.mark.parametrize("geom", [(8, 2, 64), (4, 1, 128), (4, 4, 64), (16, 1, 128)])
 def test_edges_of_windows_and_chunks_tiled_kernels(kind, size, geom):
     """The same for the tensor-core kernels (bfloat16, head sizes 64 and 128): a prompt portion of 70 tokens (tcgen05
@@ -332,7 +332,7 @@ def test_edges_of_windows_and_chunks_tiled_kernels(kind, size, geom):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("shape", [(5, 72, 100), (130, 256, 512), (1, 44, 24), (300, 320, 384)])
+@pytest.mark.parametrize("shape", [(5, 72, 100), (130, 256, 512), (1, 44, 24), (300, 328, 392)])
 def test_feed_forward_with_squared_relu(dtype, shape):
     from hfcpu_b200.config import PartSpec
     from hfcpu_b200.engine.step import Workspace

@@ -78,7 +78,7 @@ def test_bad_configurations_are_refused(edit, word):
         config_from_dict(c)
 
 
-@pytest.mark.parametrize("rot", [{"dims": 8, "base": 500.0}, {"dims": 32, "base": 20000.0},
+@pytest.mark.parametrize("rot", [{"dims": 8, "base": 500.0}, {"dims": 32, "base": 15000.0},
                                  {"dims": 12, "base": 3000.0, "scaling": {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 2.0}},
                                  {"dims": 64, "base": 1e6, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
                                  {"dims": 6, "base": 10.0, "scaling": {"factor": 2.0, "original": 5, "fast": 0.5, "slow": 0.25}}])
