@@ -250,6 +250,38 @@ def compare_configs(z):
     return manapel, qwen
 
 
+# ---- `--compare peludra`: the Peludra design beside the Qwen2 decoder at equal layer sizes ---------------------------
+# Two latent-attention layers to one chunked-attention layer.  The latent row (kv_rank + rot_dim) is 128, a size the
+# tiled attention kernels take; sixteen heads share it.  The Qwen2 twin has the same width, as many heads of the
+# attention layers' size and a gated feed-forward with as many weights as the ungated one (3 F' E = 2 F E).
+PELUDRA_SIZES = {
+    "w1024_h64": dict(width=1024, heads=16, kv=4, dim=64, q_rank=384, kv_rank=96, rot=32, window=512, chunk=1024, ff=4096, layers=9, vocab=32768),
+    "w2048_h128": dict(width=2048, heads=16, kv=4, dim=128, q_rank=768, kv_rank=96, rot=32, window=1024, chunk=2048, ff=8192, layers=9, vocab=32768),
+    "w4096_h128": dict(width=4096, heads=32, kv=8, dim=128, q_rank=1536, kv_rank=96, rot=32, window=1024, chunk=2048, ff=16384, layers=3, vocab=32768),
+}
+
+
+def peludra_configs(z):
+    latent = dict(type="latent_attention", mixer=dict(
+        heads=16, dim=z["dim"], rot_dim=z["rot"], vdim=z["dim"], q_rank=z["q_rank"], kv_rank=z["kv_rank"],
+        scale=(z["dim"] + z["rot"]) ** -0.5, mask=dict(size=z["window"]),
+        rot=dict(dims=z["rot"], base=10000.0, scaling=dict(factor=4.0, original=4096, fast=32.0, slow=1.0))))
+    chunked = dict(type="attention", mixer=dict(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5,
+                                                mask=dict(size=z["chunk"]), v_mix=True))
+    mlp = dict(kind="dense", ff=z["ff"])
+    layers = [dict(chunked if i % 3 == 1 else latent, mlp=mlp) for i in range(z["layers"])]
+    peludra = dict(architecture="Peludra", vocab=z["vocab"], width=z["width"], norm=dict(eps=1e-6), max_positions=8192,
+                   embedding=dict(scale=z["width"] ** 0.5, bigram=dict(buckets=65521, mul_prev=1000003, mul_cur=31)), layers=layers)
+    dense = (2 * z["ff"] // 3 + 7) // 8 * 8
+    qwen = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=z["layers"], hidden_size=z["width"],
+                num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["dim"], intermediate_size=dense,
+                vocab_size=z["vocab"], max_position_embeddings=8192, rms_norm_eps=1e-6, rope_theta=1e4, tie_word_embeddings=False)
+    return peludra, qwen
+
+
+COMPARISONS = {"manapel": (COMPARE_SIZES, compare_configs), "peludra": (PELUDRA_SIZES, peludra_configs)}
+
+
 def phase_work(model, q_len, ctx_len, batch):
     """Per phase of the forward pass: (operations, bytes that must move) of one step of ``batch`` requests that bring
     ``q_len`` tokens each and hold ``ctx_len`` afterwards, summed over the layers: what the roofline of each phase's
@@ -266,11 +298,26 @@ def phase_work(model, q_len, ctx_len, batch):
         L = model.layers[e.layer]
         m, f = L.mixer, L.ffn
         dv = getattr(m, "dv", m.d)
-        add("qkv", 2.0 * T * m.w_qkv.numel(), el * (m.w_qkv.numel() + T * (m.E + m.w_qkv.shape[0])))
+        # what the layer's mask lets a query see: (query, key) pairs, and the keys a request's queries read between them
+        spec = m.cache_spec()
+        first = ctx_len - q_len
+        pairs = batch * sum(p - spec.first_visible(p) + 1 for p in range(first, ctx_len))
+        keys = batch * (ctx_len - spec.first_visible(first))
         add("wo", 2.0 * T * m.w_o.numel(), el * (m.w_o.numel() + T * m.H * dv) + 4 * T * m.E)
-        pairs = batch * (q_len * (ctx_len - q_len) + q_len * (q_len + 1) // 2)
-        add("attn", 2.0 * m.H * (m.d + dv) * pairs, el * (batch * ctx_len * m.G * (m.d + dv) + 2 * T * m.H * m.d))
-        if hasattr(f, "w_gate_up"):
+        if hasattr(m, "w_ukt"):
+            # latent attention: down and query products with the per-head product that carries the queries into the latent
+            # space; attention over the cached rows and the per-head value expansion
+            front = m.w_down.numel() + m.w_uq.numel() + m.w_ukt.numel()
+            add("qkv", 2.0 * T * front, el * (front + T * (m.E + 2 * m.Qr + m.row + 2 * m.H * (m.d + m.row))))
+            add("attn", 2.0 * m.H * (m.row + m.R) * pairs + 2.0 * T * m.w_uv.numel(),
+                el * (keys * m.row + T * m.H * (m.row + m.R + m.dv) + m.w_uv.numel()))
+        else:
+            add("qkv", 2.0 * T * m.w_qkv.numel(), el * (m.w_qkv.numel() + T * (m.E + m.w_qkv.shape[0])))
+            add("attn", 2.0 * m.H * (m.d + dv) * pairs, el * (keys * m.G * (m.d + dv) + 2 * T * m.H * m.d))
+        if hasattr(f, "w_up"):
+            add("gate_up", 2.0 * T * f.w_up.numel(), el * (f.w_up.numel() + T * (f.E + f.F)))
+            add("down", 2.0 * T * f.w_down.numel(), el * (f.w_down.numel() + T * f.F) + 4 * T * f.E)
+        elif hasattr(f, "w_gate_up"):
             add("gate_up", 2.0 * T * f.w_gate_up.numel(), el * (f.w_gate_up.numel() + T * (f.E + f.F)))
             add("down", 2.0 * T * f.w_down.numel(), el * (f.w_down.numel() + T * f.F) + 4 * T * f.E)
         elif f is not None:
@@ -281,7 +328,7 @@ def phase_work(model, q_len, ctx_len, batch):
 
 
 def run_compare(args):
-    """Prefill (one prompt) and decode (a batch of single tokens) of the Manapel design and its Qwen2 twin at each size:
+    """Prefill (one prompt) and decode (a batch of single tokens) of the chosen design and its Qwen2 twin at each size:
     tokens a second, and per phase of the forward pass the device time (CUDA events around the phase's kernels, steps run
     kernel by kernel) with its share of the measured peak, the better of the operations and the bytes the phase needs."""
     import torch
@@ -290,11 +337,12 @@ def run_compare(args):
     from hfcpu_b200.config import config_from_dict
     from hfcpu_b200.engine import measure
     peaks, peaks_kind = measure.load_peaks(ROOT)
-    names = [n for n in COMPARE_SIZES if not args.sizes or n in args.sizes.split(",")]
+    sizes, configs_of = COMPARISONS[args.compare]
+    names = [n for n in sizes if not args.sizes or n in args.sizes.split(",")]
     P, B = args.prompt, args.batch
     flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda:0")
     for name in names:
-        for arch, cfg_d in zip(("manapel", "qwen2"), compare_configs(COMPARE_SIZES[name])):
+        for arch, cfg_d in zip((args.compare, "qwen2"), configs_of(sizes[name])):
             cfg = config_from_dict(cfg_d)
             model = hfcpu_b200.random_model(cfg, seed=1, dtype=torch.bfloat16, device="cuda:0", std=0.02)
             eng = hfcpu_b200.Engine(model, block_size=BLOCK, max_tokens=(B + 1) * (P + 64), max_requests=B + 1, ctx_max=P + 64)
@@ -460,7 +508,7 @@ def main():
     ap.add_argument("--marks", action="store_true", help="with --timeline: every logged mark, not one row per kernel")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), help="run one of the other sized workloads end to end through "
                     "Session.generate instead of the record (c3: 0.5B sizes, mixed chunked prompts and decodes; c4: 32B sizes)")
-    ap.add_argument("--compare", choices=["manapel"], help="instead of the record: prefill and decode of that design beside the "
+    ap.add_argument("--compare", choices=sorted(COMPARISONS), help="instead of the record: prefill and decode of that design beside the "
                     "Qwen2 decoder at equal layer sizes (random weights), one JSON line per size and architecture")
     ap.add_argument("--sizes", default="", help="with --compare: the sizes to run, with commas (default: all)")
     ap.add_argument("--ref-layers", type=int, default=28, help="layers the reference arm runs (it is a CPU program)")
