@@ -209,9 +209,15 @@ int hfb_latent_query_rope(const float *src, int splits, const float *cos_sin, in
                           void *q_plain, void *q_att, int out_dt, int T, int H, int d, int rot, int att_row, int att_col,
                           hfb_stream s);
 
+/* The two steps above and the per-head product below in one kernel, bfloat16: q_att [T, H, kv_rank + rot] receives, per
+ * head, w_ukt[h] (bfloat16 [kv_rank, d]) times the head's plain part (rounded to bfloat16) in its first kv_rank columns and
+ * the rotated part behind them. */
+int hfb_latent_query_absorb(const float *src, int splits, const float *cos_sin, int n_positions, const int32_t *positions,
+                            const void *w_ukt, void *q_att, int T, int H, int d, int rot, int kv_rank, hfb_stream s);
+
 /* A product per head: out[t, h, n] = sum_k w[h, n, k] * in[t, h, k], n < N, k < K; rows of `in` hold H heads in_row
  * apart from column 0, rows of `out` H heads out_row apart (in_row >= K, out_row >= N: a head's result may land in the
- * first N columns of a wider row).  float32 sums, any mix of element types. */
+ * first N columns of a wider row).  float32 sums; operands all bfloat16 (tensor cores) or all float32. */
 int hfb_headwise_linear(const void *in, int in_dt, const void *w, int w_dt, void *out, int out_dt, int T, int H, int N,
                         int K, int in_row, int out_row, hfb_stream s);
 

@@ -5,7 +5,7 @@
 // through the head's value expansion (Wuv_h).  This file holds what stands between the products and the attention
 // kernel: the tail of the down product (two norms, rotation, cache write), the tail of the query product (rotation,
 // split) and the per-head product that serves both Wuk_h^T and Wuv_h.  Norms, rotation and sums are float32.
-#include "common.cuh"
+#include "attention_common.cuh"
 
 static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
 
@@ -155,6 +155,145 @@ headwise_linear_kernel(const TI *in, const TW *w, TO *out, int T, int H, int N, 
         }
 }
 
+// The float32 run takes the kernel above; bfloat16 operands take the same product on the tensor cores (mma.sync.m16n8k16, bfloat16 operands, float32 sums): a block of four warps takes
+// 64 tokens x 64 outputs of one head, each warp 16 tokens; pieces of 128 of k pass through shared memory (rows padded by
+// 16 bytes, so that the eight rows of an ldmatrix fall into different banks).  MODE 1 is the tail of latent attention's
+// query product in one kernel: its A operand is the plain part of the head's query, read as the float32 (partial) sums of
+// that product and rounded to bfloat16 on the way into shared memory, and the head's rotated part is rotated and stored
+// beside the result (by the blocks of the first output tile), so that neither a rotation kernel nor a buffer of plain
+// parts stands between the query product and attention.
+constexpr int HM_T = 64, HM_N = 64, HM_K = 128, HM_KP = HM_K + 8;
+
+template <int MODE>
+__global__ void __launch_bounds__(128)
+headwise_mma_kernel(const __nv_bfloat16 *in, const float *src, int splits, const __nv_bfloat16 *w, __nv_bfloat16 *out, int T,
+                    int H, int N, int K, int in_row, int out_row, const float *cos_sin, int n_positions,
+                    const int32_t *positions, int rot, int att_col, int *err)
+{
+    __shared__ __align__(16) __nv_bfloat16 As[HM_T][HM_KP];
+    __shared__ __align__(16) __nv_bfloat16 Ws[HM_N][HM_KP];
+    const int t0 = blockIdx.x * HM_T, n0 = blockIdx.y * HM_N, h = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const __nv_bfloat16 *wh = w + (size_t)h * N * K;
+    const bool w_vec = (K & 7) == 0 && ((uintptr_t)w & 15) == 0;
+    const size_t C = (size_t)H * in_row, plane = (size_t)T * C;          // MODE 1: a row of the product, one partial sum of it
+    float acc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+    for (int k0 = 0; k0 < K; k0 += HM_K) {
+        // the head's weights: they do not depend on the kernel in front, so the first piece is fetched before the wait
+        for (int i = threadIdx.x; i < HM_N * (HM_K / 8); i += 128) {
+            const int r = i / (HM_K / 8), c = (i % (HM_K / 8)) * 8;
+            const int n = n0 + r, k = k0 + c;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (n < N && k < K) {
+                if (w_vec) v = *(const uint4 *)(wh + (size_t)n * K + k);
+                else {
+                    __nv_bfloat16 *e = (__nv_bfloat16 *)&v;
+                    for (int j = 0; j < 8 && k + j < K; j++) e[j] = wh[(size_t)n * K + k + j];
+                }
+            }
+            *(uint4 *)&Ws[r][c] = v;
+        }
+        if (k0 == 0) pdl_sync();
+        if (MODE == 0) {
+            const bool a_vec = (in_row & 7) == 0 && (K & 7) == 0 && ((uintptr_t)in & 15) == 0;
+            for (int i = threadIdx.x; i < HM_T * (HM_K / 8); i += 128) {
+                const int r = i / (HM_K / 8), c = (i % (HM_K / 8)) * 8;
+                const int t = t0 + r, k = k0 + c;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (t < T && k < K) {
+                    const __nv_bfloat16 *p = in + ((size_t)t * H + h) * in_row + k;
+                    if (a_vec) v = *(const uint4 *)p;
+                    else {
+                        __nv_bfloat16 *e = (__nv_bfloat16 *)&v;
+                        for (int j = 0; j < 8 && k + j < K; j++) e[j] = p[j];
+                    }
+                }
+                *(uint4 *)&As[r][c] = v;
+            }
+        } else {
+            const bool a_vec = (in_row & 3) == 0 && (K & 3) == 0 && ((uintptr_t)src & 15) == 0;
+            for (int i = threadIdx.x; i < HM_T * (HM_K / 4); i += 128) {
+                const int r = i / (HM_K / 4), c = (i % (HM_K / 4)) * 4;
+                const int t = t0 + r, k = k0 + c;
+                float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (t < T && k < K) {
+                    const float *p = src + (size_t)t * C + (size_t)h * in_row + k;
+                    if (a_vec) {
+                        for (int sp = 0; sp < splits; sp++) {
+                            const float4 g = *(const float4 *)(p + (size_t)sp * plane);
+                            f.x += g.x; f.y += g.y; f.z += g.z; f.w += g.w;
+                        }
+                    } else {
+                        float *e = (float *)&f;
+                        for (int j = 0; j < 4 && k + j < K; j++)
+                            for (int sp = 0; sp < splits; sp++) e[j] += p[(size_t)sp * plane + j];
+                    }
+                }
+                uint2 v;
+                v.x = pack_bf16(f.x, f.y);
+                v.y = pack_bf16(f.z, f.w);
+                *(uint2 *)&As[r][c] = v;
+            }
+        }
+        __syncthreads();
+        const int k_here = min(HM_K, K - k0);
+        const uint32_t a_base = (uint32_t)__cvta_generic_to_shared(&As[warp * 16 + (lane & 15)][(lane >> 4) * 8]);
+        const uint32_t b_base = (uint32_t)__cvta_generic_to_shared(&Ws[(lane & 7) + ((lane >> 4) << 3)][((lane >> 3) & 1) * 8]);
+        for (int kk = 0; kk < k_here; kk += 16) {
+            uint32_t a[4];
+            ldsm_x4(a_base + kk * 2, a[0], a[1], a[2], a[3]);
+#pragma unroll
+            for (int nn = 0; nn < 8; nn += 2) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(b_base + (uint32_t)(nn * 8 * HM_KP + kk) * 2, b0, b1, b2, b3);
+                mma_bf16(acc[nn], a, b0, b1);
+                mma_bf16(acc[nn + 1], a, b2, b3);
+            }
+        }
+        __syncthreads();
+    }
+    // C fragment: rows lane / 4 and + 8 of the warp's 16 tokens, columns 2 (lane % 4) and + 1 of each group of 8 outputs
+    const bool pair_ok = (out_row & 1) == 0 && ((uintptr_t)out & 3) == 0;
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        const int t = t0 + warp * 16 + (lane >> 2) + half * 8;
+        if (t >= T) continue;
+        __nv_bfloat16 *o = out + ((size_t)t * H + h) * out_row;
+#pragma unroll
+        for (int nn = 0; nn < 8; nn++) {
+            const int n = n0 + nn * 8 + (lane & 3) * 2;
+            const float x = acc[nn][half * 2], y = acc[nn][half * 2 + 1];
+            if (n + 1 < N && pair_ok) *(uint32_t *)(o + n) = pack_bf16(x, y);
+            else {
+                if (n < N) o[n] = __float2bfloat16_rn(x);
+                if (n + 1 < N) o[n + 1] = __float2bfloat16_rn(y);
+            }
+        }
+    }
+    if (MODE == 1 && blockIdx.y == 0 && rot > 0) {
+        // the head's rotated part: columns K .. K + rot of its piece of the product's row
+        const int half_rot = rot / 2;
+        for (int i = threadIdx.x; i < HM_T * half_rot; i += 128) {
+            const int t = t0 + i / half_rot, j = i % half_rot;
+            if (t >= T) break;
+            int pos = positions[t];
+            if (pos < 0 || pos >= n_positions) { atomicOr(err, HFB_ERR_POSITION); pos = 0; }
+            const float *p = src + (size_t)t * C + (size_t)h * in_row + K + 2 * j;
+            float a = 0.f, b = 0.f;
+            for (int sp = 0; sp < splits; sp++) { a += p[(size_t)sp * plane]; b += p[(size_t)sp * plane + 1]; }
+            const float *cs = cos_sin + ((size_t)pos * half_rot + j) * 2;
+            float lo, hi;
+            rope_pair(a, b, cs[0], cs[1], lo, hi);
+            __nv_bfloat16 *o = out + ((size_t)t * H + h) * out_row + att_col + 2 * j;
+            o[0] = __float2bfloat16_rn(lo);
+            o[1] = __float2bfloat16_rn(hi);
+        }
+    }
+}
+
 }  // namespace hfb
 
 using namespace hfb;
@@ -210,12 +349,30 @@ extern "C" int hfb_headwise_linear(const void *in, int in_dt, const void *w, int
     if (H > 65535 || (N + HW_NT - 1) / HW_NT > 65535) return fail(HFB_ENOTSUP, "headwise_linear: sizes exceed the grid limit");
     if (in_dt != out_dt || (in_dt == HFB_F32) != (w_dt == HFB_F32))
         return fail(HFB_ENOTSUP, "headwise_linear: operands are all float32 or all bfloat16");
+    if (in_dt == HFB_BF16) {
+        const dim3 mgrid((T + HM_T - 1) / HM_T, (N + HM_N - 1) / HM_N, H);
+        g_launch_err = launch_pdl(headwise_mma_kernel<0>, mgrid, dim3(128), 0, (cudaStream_t)s, (const __nv_bfloat16 *)in, (const float *)nullptr, 1,
+                                  (const __nv_bfloat16 *)w, (__nv_bfloat16 *)out, T, H, N, K, in_row, out_row, (const float *)nullptr, 0,
+                                  (const int32_t *)nullptr, 0, 0, error_word());
+        return check_pdl_launch(g_launch_err, "headwise_linear");
+    }
     const dim3 grid((T + HW_TT - 1) / HW_TT, (N + HW_NT - 1) / HW_NT, H);
-    if (in_dt == HFB_F32)
-        g_launch_err = launch_pdl(headwise_linear_kernel<float, float, float>, grid, dim3(256), 0, (cudaStream_t)s, (const float *)in, (const float *)w,
-                                  (float *)out, T, H, N, K, in_row, out_row);
-    else
-        g_launch_err = launch_pdl(headwise_linear_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, grid, dim3(256), 0, (cudaStream_t)s,
-                                  (const __nv_bfloat16 *)in, (const __nv_bfloat16 *)w, (__nv_bfloat16 *)out, T, H, N, K, in_row, out_row);
+    g_launch_err = launch_pdl(headwise_linear_kernel<float, float, float>, grid, dim3(256), 0, (cudaStream_t)s, (const float *)in, (const float *)w,
+                              (float *)out, T, H, N, K, in_row, out_row);
     return check_pdl_launch(g_launch_err, "headwise_linear");
+}
+
+extern "C" int hfb_latent_query_absorb(const float *src, int splits, const float *cos_sin, int n_positions, const int32_t *positions,
+                                       const void *w_ukt, void *q_att, int T, int H, int d, int rot, int kv_rank, hfb_stream s)
+{
+    if (T <= 0) return HFB_OK;
+    if (splits < 1 || H <= 0 || d <= 0 || kv_rank <= 0 || rot < 0 || (rot & 1) || !src || !w_ukt || !q_att)
+        return fail(HFB_EINVAL, "latent_query_absorb: bad arguments (H=%d d=%d rot=%d kv_rank=%d)", H, d, rot, kv_rank);
+    if (rot > 0 && (!cos_sin || !positions)) return fail(HFB_EINVAL, "latent_query_absorb: rotation needs a table and positions");
+    if (H > 65535) return fail(HFB_ENOTSUP, "latent_query_absorb: sizes exceed the grid limit");
+    const dim3 grid((T + HM_T - 1) / HM_T, (kv_rank + HM_N - 1) / HM_N, H);
+    g_launch_err = launch_pdl(headwise_mma_kernel<1>, grid, dim3(128), 0, (cudaStream_t)s, (const __nv_bfloat16 *)nullptr, src, splits,
+                              (const __nv_bfloat16 *)w_ukt, (__nv_bfloat16 *)q_att, T, H, kv_rank, d, d + rot, kv_rank + rot, cos_sin, n_positions,
+                              positions, rot, kv_rank, error_word());
+    return check_pdl_launch(g_launch_err, "latent_query_absorb");
 }

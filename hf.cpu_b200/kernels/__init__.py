@@ -385,6 +385,26 @@ def linear_latent_query(a, w, buf, cos_sin, positions, q_plain, q_att, H, d, rot
     backend().linear_latent_query(a, w, buf, cos_sin, positions, q_plain, q_att, int(H), int(d), int(rot), int(att_col))
 
 
+def linear_latent_query_absorb(a, w_uq, buf, cos_sin, positions, w_ukt, q_plain, q_att, H, d, rot) -> None:
+    """Latent attention's query, ready for attention over the cached rows: ``q = a @ w_uq.T`` (H heads of [d plain | rot
+    rotated]); per head, ``q_att`` [T, H * (kv_rank + rot)] receives ``w_ukt[h] @ q_plain`` (w_ukt [H, kv_rank, d]) in its
+    first kv_rank columns and the rotated part behind them.  One kernel behind the product in bfloat16; else
+    :func:`linear_latent_query` and :func:`headwise_linear` with ``q_plain`` [T, H * d] between them."""
+    R = w_ukt.shape[1]
+    _need(w_ukt.shape == (H, R, d) and q_att.shape == (a.shape[0], H * (R + rot)) and w_ukt.dtype == q_att.dtype,
+          "linear_latent_query_absorb: shape mismatch")
+    b = backend()
+    if hasattr(b, "linear_latent_query_absorb") and q_att.dtype == torch.bfloat16:
+        _need(w_uq.shape[0] == H * (d + rot) and a.shape[1] == w_uq.shape[1] and buf.shape == (a.shape[0], w_uq.shape[0])
+              and buf.dtype == torch.float32, "linear_latent_query_absorb: shape mismatch")
+        _need(rot % 2 == 0 and (rot == 0 or (cos_sin is not None and cos_sin.shape[1:] == (rot // 2, 2) and cos_sin.dtype == torch.float32)),
+              "linear_latent_query_absorb: cos/sin table must be float32 [positions, rot/2, 2]")
+        b.linear_latent_query_absorb(a, w_uq, buf, cos_sin, positions, w_ukt, q_att, int(H), int(d), int(rot))
+        return
+    linear_latent_query(a, w_uq, buf, cos_sin, positions, q_plain, q_att, H, d, rot, R)
+    headwise_linear(q_plain, w_ukt, q_att, H, d, R + rot)
+
+
 def headwise_linear(x, w, out, H: int, in_row: int, out_row: int) -> None:
     """A product per head: out[t, h, :N] = w[h] @ x[t, h, :K] with w [H, N, K]; a row of ``x`` holds H heads ``in_row``
     apart, a row of ``out`` H heads ``out_row`` apart (a head's result may be the first N columns of a wider row)."""

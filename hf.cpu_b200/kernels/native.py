@@ -423,6 +423,13 @@ class NativeBackend:
             _p(q_att), c_int(_dt(q_att)), c_int(a.shape[0]), c_int(H), c_int(d), c_int(rot), c_int(q_att.shape[1] // H), c_int(att_col),
             self._stream()), "latent_query_rope")
 
+    def linear_latent_query_absorb(self, a, w_uq, buf, cos_sin, positions, w_ukt, q_att, H, d, rot):
+        self._on_gpu(a, w_uq, buf, cos_sin, positions, w_ukt, q_att)
+        src, splits = self._product_sums(a, w_uq, buf)
+        self._check(self.lib.hfb_latent_query_absorb(
+            _p(src), c_int(splits), _p(cos_sin), c_int(cos_sin.shape[0] if cos_sin is not None else 0), _p(positions), _p(w_ukt),
+            _p(q_att), c_int(a.shape[0]), c_int(H), c_int(d), c_int(rot), c_int(w_ukt.shape[1]), self._stream()), "latent_query_absorb")
+
     def headwise_linear(self, x, w, out, H, in_row, out_row):
         self._on_gpu(x, w, out)
         self._check(self.lib.hfb_headwise_linear(_p(x), c_int(_dt(x)), _p(w), c_int(_dt(w)), _p(out), c_int(_dt(out)), c_int(x.shape[0]),

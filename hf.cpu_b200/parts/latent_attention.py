@@ -114,9 +114,8 @@ class LatentAttention(OutputProduct, Mixer):
             kernels.linear_latent_split(xn, self.w_down, down, self.norm_q, self.norm_kv, self.eps, cos_sin, ctx.positions,
                                         meta.slots, cq, cache.k, self.Qr, self.R, self.dr)
             q32 = ctx.buf("lat_q32", (T, self.H * (self.d + self.dr)), torch.float32)
-            kernels.linear_latent_query(cq, self.w_uq, q32, cos_sin, ctx.positions, q_plain, q_att, self.H, self.d, self.dr,
-                                        self.R)
-            kernels.headwise_linear(q_plain, self.w_ukt, q_att, self.H, self.d, self.row)
+            kernels.linear_latent_query_absorb(cq, self.w_uq, q32, cos_sin, ctx.positions, self.w_ukt, q_plain, q_att, self.H,
+                                               self.d, self.dr)
         whole_row = kernels.tiled_attention_takes(dt, self.row, meta.block_size)
         out_row = self.row if whole_row else self.R
         lat = ctx.buf("lat_out", (T, self.H * out_row), dt)

@@ -199,6 +199,18 @@ def test_latent_tails_and_per_head_products(dtype, geom):
     s_expanded = np.einsum("thd,jhd->htj", f64(q_plain).reshape(T, H, d), k_plain)
     s_latent = np.einsum("thr,jr->htj", want_lat, want_c)
     assert np.abs(s_expanded - s_latent).max() < 1e-9 * np.abs(s_expanded).max()
+    # the query product, the rotation and the per-head product behind one call (one kernel in bfloat16)
+    fused = torch.zeros(T, H * (R + dr), dtype=dt, device=DEV)
+    K().linear_latent_query_absorb(cq, w_uq, torch.empty(T, H * (d + dr), dtype=torch.float32, device=DEV), cs, positions, ukt,
+                                   torch.empty(T, H * d, dtype=dt, device=DEV), fused, H, d, dr)
+    assert rel(fused, q_att.double().cpu()) < (1e-6 if dtype == "float32" else 4e-3)
+    # many tokens: every tile of the tensor-core form, tokens beyond a tile's end
+    for many in (70, 130):
+        xin = dev(r.standard_normal((many, H * (R + dr))), dt)
+        wide = torch.zeros(many, H * dv, dtype=dt, device=DEV)
+        w_uv_m = dev(0.3 * r.standard_normal((H, dv, R)), dt)
+        K().headwise_linear(xin, w_uv_m, wide, H, R + dr, dv)
+        assert rel(wide.view(many, H, dv), np.einsum("thr,hvr->thv", f64(xin).reshape(many, H, R + dr)[..., :R], f64(w_uv_m))) < KTOL[dtype] * 2
     # the value expansion reads the first R columns of a wider row
     w_uv = dev(0.3 * r.standard_normal((H * dv, R)), dt).view(H, dv, R)
     heads = torch.zeros(T, H * dv, dtype=dt, device=DEV)
