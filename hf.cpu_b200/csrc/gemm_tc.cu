@@ -220,8 +220,17 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32
             }
         }
         if (p.mode == EPI_STORE && p.act) {
+            // the choice of the activation is made once per chunk, not once per value
+            if (p.act == HFB_ACT_RELU2) {
 #pragma unroll
-            for (int i = 0; i < 16; i++) f[i] = epi_act(f[i], p.act);
+                for (int i = 0; i < 16; i++) { const float r = fmaxf(f[i], 0.f); f[i] = r * r; }
+            } else if (p.act == HFB_ACT_RELU) {
+#pragma unroll
+                for (int i = 0; i < 16; i++) f[i] = fmaxf(f[i], 0.f);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; i++) f[i] = epi_act(f[i], p.act);
+            }
         }
         if (p.mode == EPI_PARTIAL) {
             float *dst = p.partial + (size_t)split * p.M * p.N + o;
