@@ -172,11 +172,16 @@ headwise_mma_kernel(const __nv_bfloat16 *in, const float *src, int splits, const
 {
     __shared__ __align__(16) __nv_bfloat16 As[HM_T][HM_KP];
     __shared__ __align__(16) __nv_bfloat16 Ws[HM_N][HM_KP];
-    const int t0 = blockIdx.x * HM_T, n0 = blockIdx.y * HM_N, h = blockIdx.z;
+    const int t0 = blockIdx.x * HM_T, h = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const __nv_bfloat16 *wh = w + (size_t)h * N * K;
     const bool w_vec = (K & 7) == 0 && ((uintptr_t)w & 15) == 0;
     const size_t C = (size_t)H * in_row, plane = (size_t)T * C;          // MODE 1: a row of the product, one partial sum of it
+    // A block walks the output tiles gridDim.y apart.  Where all of k fits one piece (the launch then has one block per
+    // token tile and head), the tokens' piece is fetched once and stays in shared memory for every output tile.
+    const bool a_stays = K <= HM_K;
+    bool first_piece = true;
+    for (int n0 = blockIdx.y * HM_N; n0 < N; n0 += gridDim.y * HM_N) {
     float acc[8][4];
 #pragma unroll
     for (int i = 0; i < 8; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
@@ -196,8 +201,11 @@ headwise_mma_kernel(const __nv_bfloat16 *in, const float *src, int splits, const
             }
             *(uint4 *)&Ws[r][c] = v;
         }
-        if (k0 == 0) pdl_sync();
-        if (MODE == 0) {
+        if (first_piece) pdl_sync();
+        const bool fetch_a = first_piece || !a_stays;
+        first_piece = false;
+        if (!fetch_a) {
+        } else if (MODE == 0) {
             const bool a_vec = (in_row & 7) == 0 && (K & 7) == 0 && ((uintptr_t)in & 15) == 0;
             for (int i = threadIdx.x; i < HM_T * (HM_K / 8); i += 128) {
                 const int r = i / (HM_K / 8), c = (i % (HM_K / 8)) * 8;
@@ -215,6 +223,7 @@ headwise_mma_kernel(const __nv_bfloat16 *in, const float *src, int splits, const
             }
         } else {
             const bool a_vec = (in_row & 3) == 0 && (K & 3) == 0 && ((uintptr_t)src & 15) == 0;
+#pragma unroll 4
             for (int i = threadIdx.x; i < HM_T * (HM_K / 4); i += 128) {
                 const int r = i / (HM_K / 4), c = (i % (HM_K / 4)) * 4;
                 const int t = t0 + r, k = k0 + c;
@@ -273,6 +282,7 @@ headwise_mma_kernel(const __nv_bfloat16 *in, const float *src, int splits, const
             }
         }
     }
+    }
     if (MODE == 1 && blockIdx.y == 0 && rot > 0) {
         // the head's rotated part: columns K .. K + rot of its piece of the product's row
         const int half_rot = rot / 2;
@@ -297,6 +307,11 @@ headwise_mma_kernel(const __nv_bfloat16 *in, const float *src, int splits, const
 }  // namespace hfb
 
 using namespace hfb;
+
+// Blocks per (token tile, head): one that walks all output tiles with the tokens' piece resident, where there are token
+// tiles enough to fill the SMs and all of k fits one piece; else one per output tile (few tokens: the blocks only wait for
+// their weights, and side by side they wait once).
+static int headwise_tiles_y(int T, int N, int K) { return (K <= HM_K && T >= 512) ? 1 : (N + HM_N - 1) / HM_N; }
 
 extern "C" int hfb_latent_split(const float *src, int splits, const float *q_w, const float *kv_w, float eps, const float *cos_sin,
                                 int n_positions, const int32_t *positions, const int32_t *slots, void *cq_out, void *cache,
@@ -350,7 +365,7 @@ extern "C" int hfb_headwise_linear(const void *in, int in_dt, const void *w, int
     if (in_dt != out_dt || (in_dt == HFB_F32) != (w_dt == HFB_F32))
         return fail(HFB_ENOTSUP, "headwise_linear: operands are all float32 or all bfloat16");
     if (in_dt == HFB_BF16) {
-        const dim3 mgrid((T + HM_T - 1) / HM_T, (N + HM_N - 1) / HM_N, H);
+        const dim3 mgrid((T + HM_T - 1) / HM_T, headwise_tiles_y(T, N, K), H);
         g_launch_err = launch_pdl(headwise_mma_kernel<0>, mgrid, dim3(128), 0, (cudaStream_t)s, (const __nv_bfloat16 *)in, (const float *)nullptr, 1,
                                   (const __nv_bfloat16 *)w, (__nv_bfloat16 *)out, T, H, N, K, in_row, out_row, (const float *)nullptr, 0,
                                   (const int32_t *)nullptr, 0, 0, error_word());
@@ -370,7 +385,7 @@ extern "C" int hfb_latent_query_absorb(const float *src, int splits, const float
         return fail(HFB_EINVAL, "latent_query_absorb: bad arguments (H=%d d=%d rot=%d kv_rank=%d)", H, d, rot, kv_rank);
     if (rot > 0 && (!cos_sin || !positions)) return fail(HFB_EINVAL, "latent_query_absorb: rotation needs a table and positions");
     if (H > 65535) return fail(HFB_ENOTSUP, "latent_query_absorb: sizes exceed the grid limit");
-    const dim3 grid((T + HM_T - 1) / HM_T, (kv_rank + HM_N - 1) / HM_N, H);
+    const dim3 grid((T + HM_T - 1) / HM_T, headwise_tiles_y(T, kv_rank, d), H);
     g_launch_err = launch_pdl(headwise_mma_kernel<1>, grid, dim3(128), 0, (cudaStream_t)s, (const __nv_bfloat16 *)nullptr, src, splits,
                               (const __nv_bfloat16 *)w_ukt, (__nv_bfloat16 *)q_att, T, H, kv_rank, d, d + rot, kv_rank + rot, cos_sin, n_positions,
                               positions, rot, kv_rank, error_word());

@@ -14,6 +14,16 @@ static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the las
 namespace hfb {
 int *error_word();
 
+__device__ __forceinline__ void store4(float *dst, float4 v) { *(float4 *)dst = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16 *dst, float4 v)
+{
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *(uint32_t *)&a;
+    u.y = *(uint32_t *)&b;
+    *(uint2 *)dst = u;
+}
+
 constexpr int RN_WARPS = 4;
 constexpr int RN_MAX_D = 256;
 
@@ -27,7 +37,7 @@ rope_norm_kv_kernel(const float *src, int splits, const void *bias, int bias_dt,
 {
     pdl_entry();
     pdl_sync_small();
-    __shared__ float buf[RN_WARPS][RN_MAX_D];
+    __shared__ __align__(16) float buf[RN_WARPS][RN_MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int units = H + 2 * G;
     const long long item = (long long)blockIdx.x * RN_WARPS + warp;
@@ -48,12 +58,30 @@ rope_norm_kv_kernel(const float *src, int splits, const void *bias, int bias_dt,
     }
     float *x = buf[warp];
     const size_t plane = (size_t)T * C;
-    for (int c = lane; c < n; c += 32) {
-        float v = bias ? load_any(bias, bias_dt, col0 + c) : 0.f;
-        const float *p = src + (size_t)t * C + col0 + c;
-        float acc = 0.f;
-        for (int s = 0; s < splits; s++) acc += p[(size_t)s * plane];
-        x[c] = acc + v;
+    // (16-byte reads where the heads' sizes allow: a warp then fetches a head of 128 values with one instruction a lane)
+    const bool vec = ((d | dv) & 3) == 0 && ((uintptr_t)src & 15) == 0;
+    if (vec) {
+        for (int c = lane * 4; c < n; c += 128) {
+            const float *p = src + (size_t)t * C + col0 + c;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < splits; s++) {
+                const float4 g = *(const float4 *)(p + (size_t)s * plane);
+                acc.x += g.x; acc.y += g.y; acc.z += g.z; acc.w += g.w;
+            }
+            if (bias) {
+                acc.x += load_any(bias, bias_dt, col0 + c); acc.y += load_any(bias, bias_dt, col0 + c + 1);
+                acc.z += load_any(bias, bias_dt, col0 + c + 2); acc.w += load_any(bias, bias_dt, col0 + c + 3);
+            }
+            *(float4 *)(x + c) = acc;
+        }
+    } else {
+        for (int c = lane; c < n; c += 32) {
+            float v = bias ? load_any(bias, bias_dt, col0 + c) : 0.f;
+            const float *p = src + (size_t)t * C + col0 + c;
+            float acc = 0.f;
+            for (int s = 0; s < splits; s++) acc += p[(size_t)s * plane];
+            x[c] = acc + v;
+        }
     }
     __syncwarp();
     if (is_value) {
@@ -86,6 +114,15 @@ rope_norm_kv_kernel(const float *src, int splits, const void *bias, int bias_dt,
         for (int c = lane; c < n; c += 32) ss = fmaf(x[c], x[c], ss);
         ss = warp_sum(ss);
         r = 1.0f / sqrtf(ss / (float)n + eps);
+    }
+    if (vec && ((uintptr_t)dst & (4 * sizeof(TO) - 1)) == 0) {
+        for (int c = lane * 4; c < n; c += 128) {
+            float4 v = *(const float4 *)(x + c);
+            v.x *= r; v.y *= r; v.z *= r; v.w *= r;
+            if (norm && w) { v.x *= w[c]; v.y *= w[c + 1]; v.z *= w[c + 2]; v.w *= w[c + 3]; }
+            store4(dst + c, v);
+        }
+        return;
     }
     if (norm && w) { for (int c = lane; c < n; c += 32) dst[c] = from_f32<TO>(x[c] * r * w[c]); }
     else { for (int c = lane; c < n; c += 32) dst[c] = from_f32<TO>(x[c] * r); }
