@@ -14,17 +14,9 @@ int *error_word();
 
 constexpr int LS_THREADS = 128;
 
-__device__ __forceinline__ float block_sum_128(float v, float *red)
-{
-    v = warp_sum(v);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-    __syncthreads();
-    const float total = red[0] + red[1] + red[2] + red[3];
-    __syncthreads();
-    return total;
-}
-
-// One block per (token, unit): unit 0 the query latent, 1 the key/value latent, 2 the rotated key part.
+// One block per token: the row [query latent | key/value latent | rotated part] is summed over the product's partial sums
+// into shared memory with 16-byte reads (where the sizes allow), both sums of squares are reduced in one go, and the three
+// parts leave in their forms: two normed and weighted, one rotated in pairs (2i, 2i + 1).
 template <typename TO>
 __global__ void __launch_bounds__(LS_THREADS)
 latent_split_kernel(const float *src, int splits, const float *q_w, const float *kv_w, float eps, const float *cos_sin,
@@ -33,46 +25,62 @@ latent_split_kernel(const float *src, int splits, const float *q_w, const float 
 {
     pdl_entry();
     pdl_sync_small();
-    extern __shared__ float x[];
-    __shared__ float red[4];
-    const int t = blockIdx.x, unit = blockIdx.y;
-    const int C = q_rank + kv_rank + rot;
-    const int col0 = unit == 0 ? 0 : (unit == 1 ? q_rank : q_rank + kv_rank);
-    const int n = unit == 0 ? q_rank : (unit == 1 ? kv_rank : rot);
-    TO *dst;
-    if (unit == 0) dst = cq_out + (size_t)t * q_rank;
-    else {
-        if (!slots) return;
-        const long long slot = slots[t];
-        if (slot < 0) return;
-        if (slot >= cache_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); return; }
-        dst = cache + (size_t)slot * (kv_rank + rot) + (unit == 1 ? 0 : kv_rank);
-    }
+    extern __shared__ __align__(16) float x[];
+    __shared__ float red[2][4];
+    const int t = blockIdx.x;
+    const int C = q_rank + kv_rank + rot, kv0 = q_rank, rot0 = q_rank + kv_rank;
     const size_t plane = (size_t)T * C;
-    const float *p = src + (size_t)t * C + col0;
-    float ss = 0.f;
-    for (int c = threadIdx.x; c < n; c += LS_THREADS) {
-        float acc = 0.f;
-        for (int s = 0; s < splits; s++) acc += p[(size_t)s * plane + c];
-        x[c] = acc;
-        ss = fmaf(acc, acc, ss);
+    const float *p = src + (size_t)t * C;
+    float ss_q = 0.f, ss_kv = 0.f;
+    const bool vec = ((q_rank | kv_rank | rot) & 3) == 0 && ((uintptr_t)src & 15) == 0;
+    if (vec) {
+        for (int c = threadIdx.x * 4; c < C; c += LS_THREADS * 4) {
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < splits; s++) {
+                const float4 g = *(const float4 *)(p + (size_t)s * plane + c);
+                a.x += g.x; a.y += g.y; a.z += g.z; a.w += g.w;
+            }
+            *(float4 *)(x + c) = a;
+            // four values never straddle two parts: every part's size is a multiple of four.  Which of the two forms runs
+            // depends on the sizes alone, so a row's sums are made in one order whatever the step looks like.
+            float q = 0.f;
+            q = fmaf(a.x, a.x, q); q = fmaf(a.y, a.y, q); q = fmaf(a.z, a.z, q); q = fmaf(a.w, a.w, q);
+            if (c < kv0) ss_q += q;
+            else if (c < rot0) ss_kv += q;
+        }
+    } else {
+        for (int c = threadIdx.x; c < C; c += LS_THREADS) {
+            float a = 0.f;
+            for (int s = 0; s < splits; s++) a += p[(size_t)s * plane + c];
+            x[c] = a;
+            if (c < kv0) ss_q = fmaf(a, a, ss_q);
+            else if (c < rot0) ss_kv = fmaf(a, a, ss_kv);
+        }
     }
-    if (unit < 2) {
-        ss = block_sum_128(ss, red);
-        const float r = 1.0f / sqrtf(ss / (float)n + eps);
-        const float *w = unit == 0 ? q_w : kv_w;
-        for (int c = threadIdx.x; c < n; c += LS_THREADS) dst[c] = from_f32<TO>(x[c] * r * w[c]);
-        return;
-    }
+    ss_q = warp_sum(ss_q);
+    ss_kv = warp_sum(ss_kv);
+    if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = ss_q; red[1][threadIdx.x >> 5] = ss_kv; }
     __syncthreads();
-    int pos = positions[t];
-    if (pos < 0 || pos >= n_positions) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_POSITION); pos = 0; }
-    const float *cs = cos_sin + (size_t)pos * (rot / 2) * 2;
-    for (int i = threadIdx.x; i < rot / 2; i += LS_THREADS) {
-        float lo, hi;
-        rope_pair(x[2 * i], x[2 * i + 1], cs[2 * i], cs[2 * i + 1], lo, hi);
-        dst[2 * i] = from_f32<TO>(lo);
-        dst[2 * i + 1] = from_f32<TO>(hi);
+    const float r_q = 1.0f / sqrtf((red[0][0] + red[0][1] + red[0][2] + red[0][3]) / (float)q_rank + eps);
+    const float r_kv = 1.0f / sqrtf((red[1][0] + red[1][1] + red[1][2] + red[1][3]) / (float)kv_rank + eps);
+    TO *cq = cq_out + (size_t)t * q_rank;
+    for (int c = threadIdx.x; c < q_rank; c += LS_THREADS) cq[c] = from_f32<TO>(x[c] * r_q * q_w[c]);
+    if (!slots) return;
+    const long long slot = slots[t];
+    if (slot < 0) return;
+    if (slot >= cache_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); return; }
+    TO *row = cache + (size_t)slot * (kv_rank + rot);
+    for (int c = threadIdx.x; c < kv_rank; c += LS_THREADS) row[c] = from_f32<TO>(x[kv0 + c] * r_kv * kv_w[c]);
+    if (rot > 0) {
+        int pos = positions[t];
+        if (pos < 0 || pos >= n_positions) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_POSITION); pos = 0; }
+        const float *cs = cos_sin + (size_t)pos * (rot / 2) * 2;
+        for (int i = threadIdx.x; i < rot / 2; i += LS_THREADS) {
+            float lo, hi;
+            rope_pair(x[rot0 + 2 * i], x[rot0 + 2 * i + 1], cs[2 * i], cs[2 * i + 1], lo, hi);
+            row[kv_rank + 2 * i] = from_f32<TO>(lo);
+            row[kv_rank + 2 * i + 1] = from_f32<TO>(hi);
+        }
     }
 }
 
@@ -322,10 +330,9 @@ extern "C" int hfb_latent_split(const float *src, int splits, const float *q_w, 
         return fail(HFB_EINVAL, "latent_split: bad arguments (q_rank=%d kv_rank=%d rot=%d)", q_rank, kv_rank, rot);
     if (rot > 0 && (!cos_sin || !positions)) return fail(HFB_EINVAL, "latent_split: rotation needs a table and positions");
     if (slots && !cache) return fail(HFB_EINVAL, "latent_split: the latent rows need a cache");
-    const int widest = q_rank > kv_rank ? (q_rank > rot ? q_rank : rot) : (kv_rank > rot ? kv_rank : rot);
-    const size_t smem = (size_t)widest * sizeof(float);
-    if (smem > 48 * 1024) return fail(HFB_ENOTSUP, "latent_split: latents above %d values are not supported", 48 * 1024 / 4);
-    const dim3 grid(T, rot > 0 ? 3 : 2);
+    const size_t smem = (size_t)(q_rank + kv_rank + rot) * sizeof(float);
+    if (smem > 40 * 1024) return fail(HFB_ENOTSUP, "latent_split: rows above %d values are not supported", 40 * 1024 / 4);
+    const dim3 grid(T);
     if (out_dt == HFB_F32)
         g_launch_err = launch_pdl(latent_split_kernel<float>, grid, dim3(LS_THREADS), smem, (cudaStream_t)s, src, splits, q_w, kv_w, eps, cos_sin,
                                   n_positions, positions, slots, (float *)cq_out, (float *)cache, (long long)cache_slots, T, q_rank, kv_rank, rot, error_word());
