@@ -4,7 +4,8 @@ Top-level keys: ``architecture`` ("Peludra"), ``vocab``, ``width``, ``norm`` ({`
 optionally ``bigram``: {``buckets``, ``mul_prev``, ``mul_cur``}}) and ``layers``.  A layer entry has ``type`` (the kind of
 mixer), ``mixer`` (its sizes) and ``mlp`` (its feed-forward, or null for none):
 
-* mixer "attention": ``heads``, ``kv_heads``, ``dim`` (query/key head), ``vdim`` (value head), ``scale`` (factor on the
+* mixer "attention": ``heads``, ``kv_heads`` (default: ``heads``), ``dim`` (query/key head), ``vdim`` (value head;
+  default: ``dim``), ``scale`` (factor on the
   scores), ``mask`` ({``size``}: chunks of that many positions; a query sees the earlier keys of its own chunk),
   optionally ``v_mix`` (true: from the second such layer on, the values are mixed with the first such layer's).  No
   biases, no rotation; queries and keys are normed per head (rms, one weight vector shared by the heads).
@@ -73,11 +74,12 @@ class PeludraConfig(ModelConfig):
             kind = L.get("type")
             m = _obj(L, "mixer", w)
             H = take_int(m, "heads", lo=1)
-            dim, vdim = take_int(m, "dim", lo=1), take_int(m, "vdim", lo=1)
+            dim = take_int(m, "dim", lo=1)
+            vdim = take_int(m, "vdim", default=dim, lo=1)
             take_float(m, "scale")
             _mask_size(m, w)
             if kind == "attention":
-                G = take_int(m, "kv_heads", lo=1)
+                G = take_int(m, "kv_heads", default=H, lo=1)
                 if H % G:
                     raise UnsupportedError(f"config.json: {w}unsupported attention geometry: {H} heads over {G} key/value heads")
                 mixes = m.get("v_mix", False)
@@ -142,8 +144,8 @@ class PeludraConfig(ModelConfig):
                 if m.get("v_mix"):
                     v_mix, mixing_seen = ("later" if mixing_seen else "first"), True
                 mixer = PartSpec("paged_attention", {
-                    "hidden_size": E, "num_heads": m["heads"], "num_kv_heads": m["kv_heads"], "head_dim": m["dim"],
-                    "v_head_dim": m["vdim"], "scale": float(m["scale"]), "qk_norm_eps": self.norm_eps,
+                    "hidden_size": E, "num_heads": m["heads"], "num_kv_heads": m.get("kv_heads", m["heads"]), "head_dim": m["dim"],
+                    "v_head_dim": m.get("vdim", m["dim"]), "scale": float(m["scale"]), "qk_norm_eps": self.norm_eps,
                     "qk_norm_weights": {"q": "q.norm", "k": "k.norm"}, "qkv_bias": False, "out_bias": False, "window": 0,
                     "chunk": size, "v_mix": v_mix, "v_mix_tensor": "vmix", "position": None, "prefix": f"{p}.mix",
                     "names": {"q": "q", "k": "k", "v": "v", "o": "o"}, "weight_suffix": "", "bias_suffix": ".b"})
@@ -159,7 +161,7 @@ class PeludraConfig(ModelConfig):
                         "scaling": dict(sc) if sc else None}))
                 mixer = PartSpec("latent_attention", {
                     "hidden_size": E, "num_heads": m["heads"], "head_dim": m["dim"], "rot_dim": m["rot_dim"],
-                    "v_head_dim": m["vdim"], "q_rank": m["q_rank"], "kv_rank": m["kv_rank"], "scale": float(m["scale"]),
+                    "v_head_dim": m.get("vdim", m["dim"]), "q_rank": m["q_rank"], "kv_rank": m["kv_rank"], "scale": float(m["scale"]),
                     "norm_eps": self.norm_eps, "window": size, "position": pos_name, "prefix": f"{p}.mix"})
             ffn = None
             if mlp is not None:

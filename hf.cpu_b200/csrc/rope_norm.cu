@@ -39,10 +39,10 @@ rope_norm_kv_kernel(const float *src, int splits, const void *bias, int bias_dt,
     pdl_sync_small();
     __shared__ __align__(16) float buf[RN_WARPS][RN_MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // a token per blockIdx.x, four of its units per blockIdx.y (no division to find them)
     const int units = H + 2 * G;
-    const long long item = (long long)blockIdx.x * RN_WARPS + warp;
-    if (item >= (long long)T * units) return;
-    const int t = (int)(item / units), u = (int)(item % units);
+    const int t = blockIdx.x, u = blockIdx.y * RN_WARPS + warp;
+    if (u >= units) return;
     const int C = H * d + G * d + G * dv;
     int col0, n;
     TO *dst;
@@ -146,13 +146,14 @@ extern "C" int hfb_rope_norm_kv_write(const float *src, int splits, const void *
     if (n_rot > 0 && (!cos_sin || !positions)) return fail(HFB_EINVAL, "rope_norm_kv_write: rotation needs a table and positions");
     if (v_mode < 0 || v_mode > 2 || (v_mode && (!v_first || G <= 0))) return fail(HFB_EINVAL, "rope_norm_kv_write: value mixing needs the first layer's values");
     if (G > 0 && slots && (!k_cache || !v_cache)) return fail(HFB_EINVAL, "rope_norm_kv_write: keys and values need a cache");
-    const long long items = (long long)T * (H + 2 * G);
-    const unsigned blocks = (unsigned)((items + RN_WARPS - 1) / RN_WARPS);
+    const int unit_blocks = (H + 2 * G + RN_WARPS - 1) / RN_WARPS;
+    if (unit_blocks > 65535) return fail(HFB_ENOTSUP, "rope_norm_kv_write: %d heads exceed the grid limit", H + 2 * G);
+    const dim3 blocks(T, unit_blocks);
     if (out_dt == HFB_F32)
-        g_launch_err = launch_pdl(rope_norm_kv_kernel<float>, dim3(blocks), dim3(RN_WARPS * 32), 0, (cudaStream_t)s, src, splits, bias, bias_dt, cos_sin, n_rot,
+        g_launch_err = launch_pdl(rope_norm_kv_kernel<float>, blocks, dim3(RN_WARPS * 32), 0, (cudaStream_t)s, src, splits, bias, bias_dt, cos_sin, n_rot,
             n_positions, positions, slots, (float *)q_out, (float *)k_cache, (float *)v_cache, (long long)cache_slots, T, H, G, d, dv, norm, eps, q_w, k_w, v_first, v_mode, v_lambda, error_word());
     else
-        g_launch_err = launch_pdl(rope_norm_kv_kernel<__nv_bfloat16>, dim3(blocks), dim3(RN_WARPS * 32), 0, (cudaStream_t)s, src, splits, bias, bias_dt, cos_sin, n_rot,
+        g_launch_err = launch_pdl(rope_norm_kv_kernel<__nv_bfloat16>, blocks, dim3(RN_WARPS * 32), 0, (cudaStream_t)s, src, splits, bias, bias_dt, cos_sin, n_rot,
             n_positions, positions, slots, (__nv_bfloat16 *)q_out, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, (long long)cache_slots, T, H, G, d, dv, norm, eps,
             q_w, k_w, v_first, v_mode, v_lambda, error_word());
     return check_pdl_launch(g_launch_err, "rope_norm_kv_write");
