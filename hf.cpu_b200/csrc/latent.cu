@@ -12,13 +12,14 @@ static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the las
 namespace hfb {
 int *error_word();
 
-constexpr int LS_THREADS = 128;
+constexpr int LS_THREADS = 128;          // threads of a block of latent_split_kernel for narrow rows; up to 512 for wide ones
+constexpr int LS_MAX_WARPS = 16;
 
 // One block per token: the row [query latent | key/value latent | rotated part] is summed over the product's partial sums
 // into shared memory with 16-byte reads (where the sizes allow), both sums of squares are reduced in one go, and the three
 // parts leave in their forms: two normed and weighted, one rotated in pairs (2i, 2i + 1).
 template <typename TO>
-__global__ void __launch_bounds__(LS_THREADS)
+__global__ void __launch_bounds__(LS_MAX_WARPS * 32)
 latent_split_kernel(const float *src, int splits, const float *q_w, const float *kv_w, float eps, const float *cos_sin,
                     int n_positions, const int32_t *positions, const int32_t *slots, TO *cq_out, TO *cache,
                     long long cache_slots, int T, int q_rank, int kv_rank, int rot, int *err)
@@ -26,7 +27,8 @@ latent_split_kernel(const float *src, int splits, const float *q_w, const float 
     pdl_entry();
     pdl_sync_small();
     extern __shared__ __align__(16) float x[];
-    __shared__ float red[2][4];
+    __shared__ float red[2][LS_MAX_WARPS];
+    const int threads = blockDim.x, warps = threads >> 5;
     const int t = blockIdx.x;
     const int C = q_rank + kv_rank + rot, kv0 = q_rank, rot0 = q_rank + kv_rank;
     const size_t plane = (size_t)T * C;
@@ -34,7 +36,7 @@ latent_split_kernel(const float *src, int splits, const float *q_w, const float 
     float ss_q = 0.f, ss_kv = 0.f;
     const bool vec = ((q_rank | kv_rank | rot) & 3) == 0 && ((uintptr_t)src & 15) == 0;
     if (vec) {
-        for (int c = threadIdx.x * 4; c < C; c += LS_THREADS * 4) {
+        for (int c = threadIdx.x * 4; c < C; c += threads * 4) {
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int s = 0; s < splits; s++) {
                 const float4 g = *(const float4 *)(p + (size_t)s * plane + c);
@@ -49,7 +51,7 @@ latent_split_kernel(const float *src, int splits, const float *q_w, const float 
             else if (c < rot0) ss_kv += q;
         }
     } else {
-        for (int c = threadIdx.x; c < C; c += LS_THREADS) {
+        for (int c = threadIdx.x; c < C; c += threads) {
             float a = 0.f;
             for (int s = 0; s < splits; s++) a += p[(size_t)s * plane + c];
             x[c] = a;
@@ -61,21 +63,23 @@ latent_split_kernel(const float *src, int splits, const float *q_w, const float 
     ss_kv = warp_sum(ss_kv);
     if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = ss_q; red[1][threadIdx.x >> 5] = ss_kv; }
     __syncthreads();
-    const float r_q = 1.0f / sqrtf((red[0][0] + red[0][1] + red[0][2] + red[0][3]) / (float)q_rank + eps);
-    const float r_kv = 1.0f / sqrtf((red[1][0] + red[1][1] + red[1][2] + red[1][3]) / (float)kv_rank + eps);
+    float sum_q = 0.f, sum_kv = 0.f;
+    for (int i = 0; i < warps; i++) { sum_q += red[0][i]; sum_kv += red[1][i]; }
+    const float r_q = 1.0f / sqrtf(sum_q / (float)q_rank + eps);
+    const float r_kv = 1.0f / sqrtf(sum_kv / (float)kv_rank + eps);
     TO *cq = cq_out + (size_t)t * q_rank;
-    for (int c = threadIdx.x; c < q_rank; c += LS_THREADS) cq[c] = from_f32<TO>(x[c] * r_q * q_w[c]);
+    for (int c = threadIdx.x; c < q_rank; c += threads) cq[c] = from_f32<TO>(x[c] * r_q * q_w[c]);
     if (!slots) return;
     const long long slot = slots[t];
     if (slot < 0) return;
     if (slot >= cache_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); return; }
     TO *row = cache + (size_t)slot * (kv_rank + rot);
-    for (int c = threadIdx.x; c < kv_rank; c += LS_THREADS) row[c] = from_f32<TO>(x[kv0 + c] * r_kv * kv_w[c]);
+    for (int c = threadIdx.x; c < kv_rank; c += threads) row[c] = from_f32<TO>(x[kv0 + c] * r_kv * kv_w[c]);
     if (rot > 0) {
         int pos = positions[t];
         if (pos < 0 || pos >= n_positions) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_POSITION); pos = 0; }
         const float *cs = cos_sin + (size_t)pos * (rot / 2) * 2;
-        for (int i = threadIdx.x; i < rot / 2; i += LS_THREADS) {
+        for (int i = threadIdx.x; i < rot / 2; i += threads) {
             float lo, hi;
             rope_pair(x[rot0 + 2 * i], x[rot0 + 2 * i + 1], cs[2 * i], cs[2 * i + 1], lo, hi);
             row[kv_rank + 2 * i] = from_f32<TO>(lo);
@@ -333,11 +337,15 @@ extern "C" int hfb_latent_split(const float *src, int splits, const float *q_w, 
     const size_t smem = (size_t)(q_rank + kv_rank + rot) * sizeof(float);
     if (smem > 40 * 1024) return fail(HFB_ENOTSUP, "latent_split: rows above %d values are not supported", 40 * 1024 / 4);
     const dim3 grid(T);
+    // The number of threads goes with the row's width only, never with the number of tokens: the order in which a row's
+    // squares are summed must not depend on what else the step holds.
+    const int row = q_rank + kv_rank + rot;
+    const dim3 block(row >= 2048 ? LS_MAX_WARPS * 32 : (row >= 768 ? 256 : LS_THREADS));
     if (out_dt == HFB_F32)
-        g_launch_err = launch_pdl(latent_split_kernel<float>, grid, dim3(LS_THREADS), smem, (cudaStream_t)s, src, splits, q_w, kv_w, eps, cos_sin,
+        g_launch_err = launch_pdl(latent_split_kernel<float>, grid, block, smem, (cudaStream_t)s, src, splits, q_w, kv_w, eps, cos_sin,
                                   n_positions, positions, slots, (float *)cq_out, (float *)cache, (long long)cache_slots, T, q_rank, kv_rank, rot, error_word());
     else
-        g_launch_err = launch_pdl(latent_split_kernel<__nv_bfloat16>, grid, dim3(LS_THREADS), smem, (cudaStream_t)s, src, splits, q_w, kv_w, eps, cos_sin,
+        g_launch_err = launch_pdl(latent_split_kernel<__nv_bfloat16>, grid, block, smem, (cudaStream_t)s, src, splits, q_w, kv_w, eps, cos_sin,
                                   n_positions, positions, slots, (__nv_bfloat16 *)cq_out, (__nv_bfloat16 *)cache, (long long)cache_slots, T, q_rank,
                                   kv_rank, rot, error_word());
     return check_pdl_launch(g_launch_err, "latent_split");

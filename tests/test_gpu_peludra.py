@@ -255,7 +255,8 @@ MASKS = {"window": lambda size: (size, lambda pos: max(0, pos - size + 1)),
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("kind,size", [("window", 44), ("window", 1), ("chunk", 208), ("chunk", 16), ("chunk", 1), ("window", 7)])
+@pytest.mark.parametrize("kind,size", [("window", 44), ("window", 1), ("chunk", 208), ("chunk", 16), ("chunk", 1), ("window", 7), ("chunk", 1000),
+                                       ("window", 400)])
 @pytest.mark.parametrize("geom", [(6, 3, 24, 40, False), (4, 1, 96, 64, True), (3, 1, 32, 24, True), (2, 1, 576, 512, True)])
 def test_edges_of_windows_and_chunks_plain_kernel(dtype, kind, size, geom):
     """One key carries a score far above the rest; it is placed just inside and just outside the mask of the last query
@@ -265,7 +266,8 @@ def test_edges_of_windows_and_chunks_plain_kernel(dtype, kind, size, geom):
     code, lo_of = MASKS[kind](size)
     last = n - 1
     lo = lo_of(last)
-    for planted in sorted({lo, lo - 1, max(lo - 2, 0), last, min(lo + 1, last)}):
+    # around the mask's edge, and far keys on both sides of page borders (inside or outside the mask as it falls)
+    for planted in sorted({lo, lo - 1, max(lo - 2, 0), last, min(lo + 1, last), 0, bs - 1, bs, 7 * bs - 1, 7 * bs, 40 * bs - 1}):
         if planted < 0:
             continue
         r = rng(planted + size)
@@ -301,7 +303,8 @@ def test_edges_of_windows_and_chunks_plain_kernel(dtype, kind, size, geom):
     K().check_device_errors()
 
 
-@pytest.mark.parametrize("kind,size", [("window", 44), ("window", 100), ("chunk", 48), ("chunk", 208), ("chunk", 64), ("chunk", 1)])
+@pytest.mark.parametrize("kind,size", [("window", 44), ("window", 100), ("chunk", 48), ("chunk", 208), ("chunk", 64), ("chunk", 1), ("chunk", 1000),
+                                       ("window", 400)])
 @pytest.mark.parametrize("geom", [(8, 2, 64), (4, 1, 128), (4, 4, 64), (16, 1, 128)])
 def test_edges_of_windows_and_chunks_tiled_kernels(kind, size, geom):
     """The same for the tensor-core kernels (bfloat16, head sizes 64 and 128): a prompt portion of 70 tokens (tcgen05
@@ -313,7 +316,7 @@ def test_edges_of_windows_and_chunks_tiled_kernels(kind, size, geom):
     code, lo_of = MASKS[kind](size)
     last = n - 1
     lo = lo_of(last)
-    for planted in sorted({lo, lo - 1, last}):
+    for planted in sorted({lo, lo - 1, last, 0, bs - 1, bs, 9 * bs - 1, 9 * bs}):
         if planted < 0:
             continue
         r = rng(planted + size + d)
